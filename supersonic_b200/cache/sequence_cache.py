@@ -34,6 +34,12 @@ class KvNeed:
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None       # None: every earlier key stays
+    value_dim: Optional[int] = None    # width of a value row; None: head_dim; 0: no value store (a mixer
+                                       # whose values are part of its key rows, such as a cached latent)
+
+    @property
+    def v_dim(self) -> int:
+        return self.head_dim if self.value_dim is None else int(self.value_dim)
 
 
 @dataclass(frozen=True)
@@ -104,7 +110,7 @@ class KvGroup:
         self.pages_per_seq = pages_per_seq
         shape = (len(entries), n_pages, need.n_kv_heads, PAGE_TOKENS, need.head_dim)
         self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        self.v = torch.zeros(shape[:-1] + (need.v_dim,), dtype=dtype, device=device)
         pin = device.type == "cuda"
         self.table_host = torch.zeros((max_slots, pages_per_seq), dtype=torch.int32, pin_memory=pin)
         self.table = torch.zeros((max_slots, pages_per_seq), dtype=torch.int32, device=device)
@@ -189,7 +195,7 @@ class SequenceCache:
         seen = set()
         for need in needs.values():
             if isinstance(need, KvNeed):
-                total += 2 * n_pages * need.n_kv_heads * PAGE_TOKENS * need.head_dim * item
+                total += n_pages * need.n_kv_heads * PAGE_TOKENS * (need.head_dim + need.v_dim) * item
                 if need not in seen:                                       # one page table a group
                     seen.add(need)
                     total += slots * pages_per_seq * 4
@@ -266,7 +272,8 @@ class SequenceCache:
 
     # ---- what parts read --------------------------------------------------------------
     def kv(self, cache_id: int):
-        """(k, v, page_table, group) of one cache entry; k and v are ``[pages, kv_heads, 64, head_dim]``."""
+        """(k, v, page_table, group) of one cache entry; k is ``[pages, kv_heads, 64, head_dim]``, v the same
+        with the need's value width (empty if that is 0)."""
         g = self._group_of[cache_id]
         i = g.index_of[cache_id]
         return g.k[i], g.v[i], g.table, g
@@ -285,7 +292,7 @@ class SequenceCache:
         total = 0
         for g in self.kv_groups:
             tokens = n if g.need.window is None else min(n, g.need.window)
-            total += len(g.entries) * 2 * tokens * g.need.n_kv_heads * g.need.head_dim * g.k.element_size()
+            total += len(g.entries) * tokens * g.need.n_kv_heads * (g.need.head_dim + g.need.v_dim) * g.k.element_size()
         return total + sum(t.shape[1] * 4 for t in self._state.values())
 
     def bytes_held(self) -> int:

@@ -40,10 +40,12 @@ class BlockSpec:
 
     kind: str                      # registered block arrangement, e.g. "pre_norm"
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: Optional[PartSpec]          # None: the layer has no feed-forward
     mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    feed_forward_norm: Optional[PartSpec]     # None: an arrangement with one norm for both sublayers
     position: Optional[PartSpec] = None   # position encoding used by the mixer
+    params: Dict[str, Any] = field(default_factory=dict)    # the arrangement's own constants
+    weights: Dict[str, str] = field(default_factory=dict)   # ... and tensors (role -> name)
 
 
 @dataclass(frozen=True)

@@ -1,6 +1,6 @@
 """One registry from an architecture's name to its configuration class.
 
-``config.json``'s ``architectures[0]`` picks the entry, everywhere in the
+``config.json``'s ``architectures[0]`` (or its ``architecture`` name) picks the entry, everywhere in the
 framework.  The reference maps CLI aliases to a family enum and dispatches with
 a ``match`` (crates/runner/src/registry.rs:41-59, main.rs:1401-1413); here the
 table is open: adding an architecture is one ``register_architecture`` call
@@ -15,6 +15,7 @@ from typing import Any, Dict, Type
 
 from .base import ConfigError, ModelSpec
 from .llama import ARCHITECTURE as _LLAMA, LlamaConfig
+from .sotavik import ARCHITECTURE as _SOTAVIK, SotavikConfig
 
 _ARCHITECTURES: Dict[str, Type] = {}
 
@@ -39,8 +40,10 @@ def lookup_architecture(name: str) -> Type:
 
 def config_from_dict(d: Dict[str, Any]):
     archs = d.get("architectures")
+    if archs is None and isinstance(d.get("architecture"), str):
+        archs = [d["architecture"]]          # the single-name spelling some designs' config.json uses
     if not archs or not isinstance(archs, list):
-        raise ConfigError("config.json has no 'architectures' list")
+        raise ConfigError("config.json has no 'architectures' list (nor an 'architecture' name)")
     return lookup_architecture(archs[0]).from_dict(d)
 
 
@@ -62,6 +65,7 @@ def spec_from_config(config) -> ModelSpec:
 
 
 register_architecture(_LLAMA, LlamaConfig)
+register_architecture(_SOTAVIK, SotavikConfig)
 
 
 _PRESET_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "presets")

@@ -42,6 +42,9 @@ LIBRARIES: Dict[str, Dict[str, List[str]]] = {
     "gemv_tc": {"sources": ["gemv_tc.cu"], "flags": [], "link": []},
     "gemm_tc": {"sources": ["gemm_tc.cu"], "flags": [], "link": []},
     "attention_decode_static": {"sources": ["attention_decode_static.cu"], "flags": [], "link": []},
+    "latent_ops": {"sources": ["latent_ops.cu"], "flags": [], "link": []},
+    "recurrence_ops": {"sources": ["recurrence_ops.cu"], "flags": [], "link": []},
+    "expert_ops": {"sources": ["expert_ops.cu"], "flags": [], "link": []},
     "random_fill": {"sources": ["random_fill.cu"], "flags": [], "link": []},
     # the host side's native core: no CUDA in it, so it is compiled by the C++ compiler alone
     "host_runtime": {"sources": ["runtime.cpp"], "flags": [], "link": [], "dir": os.path.join(os.path.dirname(_HERE), "host"),

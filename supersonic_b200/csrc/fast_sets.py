@@ -60,8 +60,11 @@ class FastKernels(PlainKernels):
             ops.rmsnorm(x, weight, eps, out, rows, pdl=pdl)
 
     def rope_append(self, qkv, cos, sin, batch, page_table, k_cache, v_cache, n_q, n_kv, head_dim,
-                    rotary_dim, page_shift, write_cache=True):
-        if ops.rope_append_vec_ok(qkv, cos, head_dim, rotary_dim, write_cache):
+                    rotary_dim, page_shift, write_cache=True, interleaved=False):
+        if interleaved:
+            super().rope_append(qkv, cos, sin, batch, page_table, k_cache, v_cache, n_q, n_kv, head_dim,
+                                rotary_dim, page_shift, write_cache, interleaved)
+        elif ops.rope_append_vec_ok(qkv, cos, head_dim, rotary_dim, write_cache):
             ops.rope_append_vec(qkv, cos, sin, batch.pos, batch.slot_of_token, page_table, k_cache, v_cache,
                                 n_q, n_kv, head_dim, page_shift)
         else:
@@ -257,6 +260,8 @@ class FastKernels(PlainKernels):
         key and value columns never go through ``qkv``)."""
         tables = getattr(position, "rotary_tables", None)
         rows = batch.n_tokens
+        if getattr(position, "interleaved", False):
+            return False                      # the fused rotations pair (i, i + half)
         if not (self.fuse_rope_prefill and tables and not batch.is_decode and rows > 64
                 and w_qkv.dtype == torch.bfloat16 and head_dim in (64, 128)):
             return False
@@ -277,6 +282,8 @@ class FastKernels(PlainKernels):
     def rope_attention(self, qkv, position, kv, batch, out, n_q, n_kv, head_dim, page_shift, window,
                        scale) -> bool:
         tables = getattr(position, "rotary_tables", None)
+        if getattr(position, "interleaved", False):
+            return False
         if not (self.fuse_rope and batch.is_decode and tables and qkv.dtype == torch.bfloat16
                 and head_dim in (32, 64, 128, 256) and qkv.stride(0) % 8 == 0):
             return False

@@ -82,9 +82,9 @@ class PlainKernels:
         return False
 
     def rope_append(self, qkv, cos, sin, batch, page_table, k_cache, v_cache, n_q, n_kv, head_dim,
-                    rotary_dim, page_shift, write_cache=True):
+                    rotary_dim, page_shift, write_cache=True, interleaved=False):
         ops.rope_append(qkv, cos, sin, batch.pos, batch.slot_of_token, page_table, k_cache, v_cache,
-                        n_q, n_kv, head_dim, rotary_dim, page_shift, write_cache)
+                        n_q, n_kv, head_dim, rotary_dim, page_shift, write_cache, interleaved)
 
     def rope_attention(self, qkv, position, kv, batch, out, n_q, n_kv, head_dim, page_shift, window,
                        scale) -> bool:
@@ -99,6 +99,66 @@ class PlainKernels:
 
     def swiglu(self, gate_up, out):
         ops.swiglu(gate_up, out)
+
+    # ---- latent attention ------------------------------------------------------------
+    def head_linear(self, x, w, out):
+        """out[t, h] = w[h] @ x[t, h]: a matrix per head (``x`` [T, H, K] and ``out`` [T, H, N] may be views
+        into wider rows, ``w`` [H, N, K])."""
+        ops.head_linear_plain(x, w, out)
+
+    def latent_prepare(self, proj, c_off, q_abs, norm_w, eps, position, batch, page_table, cache, n_heads, dim,
+                       rot_dim, kv_rank, page_shift, write_cache=True):
+        """Rotated query parts into ``q_abs``; the token's cache row [normed latent | rotated key part]."""
+        cos, sin, rot_dims = position.rotary_tables()
+        ops.latent_prepare(proj, c_off, q_abs, norm_w, eps, cos, sin, batch.pos, batch.slot_of_token, page_table,
+                           cache, n_heads, dim, rot_dim, rot_dims, kv_rank, page_shift, write_cache,
+                           getattr(position, "interleaved", False))
+
+    def latent_attention(self, q_abs, cache, batch, page_table, out, n_heads, kv_rank, rot_dim, page_shift,
+                         window, scale, sinks):
+        """Attention of every head over the one cached row per token: keys are the whole rows
+        (kv_rank + rot_dim), values their first kv_rank elements; ``sinks`` as in ``ops.attention_plain``.
+        ``out`` [T, heads x kv_rank]."""
+        ops.attention_plain(q_abs, cache, None, batch.pos, batch.slot_of_token, page_table, out, n_heads, 1,
+                            kv_rank + rot_dim, page_shift, window, scale, value_dim=kv_rank, sinks=sinks)
+
+    # ---- linear recurrence -----------------------------------------------------------
+    def gated_linear_scan(self, proj, q_off, k_off, v_off, z, z_bias, tau, q_scale, state, batch, out, n_heads,
+                          dim, vdim):
+        ops.gated_linear_scan(proj, q_off, k_off, v_off, z, z_bias, tau, q_scale, state, batch.cu_new,
+                              batch.seq_slot, out, n_heads, dim, vdim)
+
+    def head_norm_gate(self, o, weight, eps, gate, out, n_heads, vdim):
+        ops.head_norm_gate(o, weight, eps, gate, out, n_heads, vdim)
+
+    # ---- experts ---------------------------------------------------------------------
+    expert_tile_rows = 64
+
+    def route_table(self, token_ids, table, n_experts, expert_of, pair_weight):
+        ops.route_table(token_ids, table, n_experts, expert_of, pair_weight)
+
+    def group_by_expert(self, expert_of, n_experts, groups):
+        """``groups``: the dict of int32 tensors a grouped product reads (offsets, order, tile_expert,
+        tile_row0, meta) plus ``max_tiles``."""
+        ops.group_by_expert(expert_of, n_experts, groups["tile_rows"], groups["offsets"], groups["order"],
+                            groups["tile_expert"], groups["tile_row0"], groups["meta"])
+
+    def grouped_linear(self, a, gather, top, w, out, scatter, groups):
+        """Per expert group: out[rows] = a[rows] @ w[e]^T.  ``gather``: a's rows are tokens, looked up through
+        the sorted order (pair // top); ``scatter``: out's rows are pairs, written through the order."""
+        ops.grouped_gemm_plain(a, groups["order"] if gather else None, top if gather else 1, w, out,
+                               groups["order"] if scatter else None, groups["offsets"], groups["tile_expert"],
+                               groups["tile_row0"], groups["meta"], groups["max_tiles"])
+
+    def expert_combine(self, residual, y, pair_weight, top):
+        ops.expert_combine(residual, y, pair_weight, top)
+
+    # ---- streams ---------------------------------------------------------------------
+    def scale_(self, x, s):
+        ops.scale_(x, s)
+
+    def stream_mix(self, streams, weights, n_terms, out):
+        ops.stream_mix(streams, weights, n_terms, out)
 
     def add_into(self, out, x):
         ops.add_into(out, x)

@@ -133,8 +133,10 @@ def gemm_nt_plain(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulat
 def rope_append(qkv: torch.Tensor, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
                 pos: torch.Tensor, slot: torch.Tensor, page_table: torch.Tensor,
                 k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], n_q: int, n_kv: int,
-                head_dim: int, rotary_dim: int, page_shift: int, write_cache: bool = True) -> None:
-    """Rotate q (and k) of every token in place; write k and v into the paged cache entry."""
+                head_dim: int, rotary_dim: int, page_shift: int, write_cache: bool = True,
+                interleaved: bool = False) -> None:
+    """Rotate q (and k) of every token in place; write k and v into the paged cache entry.  Pairs are
+    (i, i + rotary_dim/2), or with ``interleaved`` (2i, 2i + 1)."""
     _need(qkv, "qkv", None, 2); _need(pos, "pos", torch.int32, 1); _need(slot, "slot", torch.int32, 1)
     _need(page_table, "page_table", torch.int32, 2)
     T = qkv.shape[0]
@@ -158,27 +160,43 @@ def rope_append(qkv: torch.Tensor, cos: Optional[torch.Tensor], sin: Optional[to
         _ptr(qkv), c_int(qkv.stride(0)), c_int(dtype_code(qkv.dtype)), _ptr(cos), _ptr(sin),
         c_int(table_positions), _ptr(pos), _ptr(slot), _ptr(page_table), c_int(page_table.shape[1]),
         _ptr(k_cache), _ptr(v_cache), c_int(T), c_int(n_q), c_int(n_kv), c_int(head_dim),
-        c_int(rotary_dim), c_int(page_shift), c_int(1 if write_cache else 0), _stream()), "rope_append")
+        c_int(rotary_dim), c_int(page_shift), c_int(1 if write_cache else 0), c_int(1 if interleaved else 0),
+        _stream()), "rope_append")
 
 
 def attention_plain(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, pos: torch.Tensor,
                     slot: torch.Tensor, page_table: torch.Tensor, out: torch.Tensor, n_q: int, n_kv: int,
-                    head_dim: int, page_shift: int, window: Optional[int], scale: float) -> None:
-    """Each token attends over keys [max(0, pos-window+1), pos] of its slot in the paged cache."""
+                    head_dim: int, page_shift: int, window: Optional[int], scale: float,
+                    value_dim: Optional[int] = None, sinks: Optional[torch.Tensor] = None) -> None:
+    """Each token attends over keys [max(0, pos-window+1), pos] of its slot in the paged cache.
+    ``value_dim``: width of a value and of a head's output when it differs from ``head_dim``;
+    ``v_cache`` None: a token's value is the first ``value_dim`` elements of its key row.
+    ``sinks`` (float32, one per query head): one more term exp(sink) in the softmax's denominator,
+    with no key and no value."""
+    v_dim = head_dim if value_dim is None else int(value_dim)
+    v_row = v_dim
+    if v_cache is None:
+        v_cache, v_row = k_cache, head_dim
+    if sinks is not None:
+        _need(sinks, "sinks", torch.float32, 1)
+        if sinks.shape[0] != n_q:
+            raise KernelError("attention: one sink per query head")
     _need(q, "q", None, 2); _need(out, "out", q.dtype, 2)
     _need(k_cache, "k_cache", q.dtype); _need(v_cache, "v_cache", q.dtype)
     _need(pos, "pos", torch.int32, 1); _need(slot, "slot", torch.int32, 1)
     _need(page_table, "page_table", torch.int32, 2)
     T = q.shape[0]
-    if out.shape[0] != T or out.shape[1] < n_q * head_dim or q.shape[1] < n_q * head_dim:
+    if out.shape[0] != T or out.shape[1] < n_q * v_dim or q.shape[1] < n_q * head_dim:
         raise KernelError("attention: q/out shapes")
-    if head_dim > 512 or n_q % n_kv:
-        raise KernelError(f"attention_plain: head_dim {head_dim} (max 512), heads {n_q}/{n_kv} not supported")
+    if head_dim > 1024 or v_dim > 1024 or v_dim > v_row or n_q % n_kv:
+        raise KernelError(f"attention_plain: head_dim {head_dim}, value_dim {v_dim} (max 1024), heads {n_q}/{n_kv} "
+                          "not supported")
     _check(_fn("plain_ops", "ssb_attention_plain")(
         _ptr(q), c_int(q.stride(0)), c_int(dtype_code(q.dtype)), _ptr(k_cache), _ptr(v_cache), _ptr(pos),
         _ptr(slot), _ptr(page_table), c_int(page_table.shape[1]), _ptr(out), c_int(out.stride(0)),
         c_int(T), c_int(n_q), c_int(n_kv), c_int(head_dim), c_int(page_shift),
-        c_int(int(window) if window else 0), c_float(scale), _stream()), "attention_plain")
+        c_int(int(window) if window else 0), c_float(scale), c_int(v_dim), c_int(v_row), _ptr(sinks),
+        _stream()), "attention_plain")
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool = False) -> None:
@@ -201,6 +219,193 @@ def add_into(out: torch.Tensor, x: torch.Tensor) -> None:
         raise KernelError("add_into: contiguous tensors of equal size")
     _check(_fn("plain_ops", "ssb_add_into")(
         _ptr(out), _ptr(x), c_int(dtype_code(x.dtype)), c_longlong(out.numel()), _stream()), "add_into")
+
+
+def scale_(x: torch.Tensor, s: float) -> None:
+    """x (float32, contiguous) *= s."""
+    _need(x, "x", torch.float32)
+    if not x.is_contiguous():
+        raise KernelError("scale_: a contiguous tensor")
+    _check(_fn("plain_ops", "ssb_scale")(_ptr(x), c_float(s), c_longlong(x.numel()), _stream()), "scale")
+
+
+def stream_mix(streams: torch.Tensor, weights: torch.Tensor, n_terms: int, out: torch.Tensor,
+               pdl: bool = False) -> None:
+    """out = sum_{j < n_terms} weights[j] * streams[j]: ``streams`` [n, ...] float32 contiguous, ``out`` one
+    of its planes or a tensor of a plane's size; the terms are added in the order of j."""
+    _need(streams, "streams", torch.float32); _need(weights, "weights", torch.float32, 1); _need(out, "out", torch.float32)
+    if not (streams.is_contiguous() and out.is_contiguous()) or streams.dim() < 2:
+        raise KernelError("stream_mix: contiguous tensors, streams [n, ...]")
+    plane = streams[0].numel()
+    if out.numel() != plane or not 0 < n_terms <= min(streams.shape[0], weights.shape[0]):
+        raise KernelError(f"stream_mix: {n_terms} terms of {tuple(streams.shape)} into {tuple(out.shape)}")
+    _check(_fn("plain_ops", "ssb_stream_mix")(
+        _ptr(streams), c_longlong(plane), _ptr(weights), c_int(n_terms), _ptr(out), c_longlong(plane),
+        c_int(1 if pdl else 0), _stream()), "stream_mix")
+
+
+def head_linear_plain(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, h, :] = w[h] @ x[t, h, :]: one matrix per head.  ``x`` [T, H, K] and ``out`` [T, H, N] may be
+    views into wider rows (any row and head strides, last dim contiguous); ``w`` [H, N, K] contiguous."""
+    _need(w, "w", x.dtype, 3)
+    if not (x.is_cuda and out.is_cuda) or x.dim() != 3 or out.dim() != 3:
+        raise KernelError("head_linear: x and out must be CUDA tensors [T, H, width]")
+    T, H, K = x.shape
+    N = w.shape[1]
+    if tuple(w.shape) != (H, N, K) or tuple(out.shape) != (T, H, N) or not w.is_contiguous():
+        raise KernelError(f"head_linear: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+    if x.stride(2) != 1 or out.stride(2) != 1:
+        raise KernelError("head_linear: x and out must be contiguous in their last dim")
+    _check(_fn("plain_ops", "ssb_gemm_nt_plain_batched")(
+        _ptr(x), c_int(x.stride(0)), c_longlong(x.stride(1)), _ptr(w), c_int(K), c_longlong(N * K),
+        c_int(dtype_code(x.dtype)), _ptr(out), c_int(out.stride(0)), c_longlong(out.stride(1)),
+        c_int(dtype_code(out.dtype)), c_int(H), c_int(T), c_int(N), c_int(K), _stream()), "head_linear")
+
+
+# ---- latent attention ------------------------------------------------------------------
+def latent_prepare(proj: torch.Tensor, c_off: int, q_abs: torch.Tensor, norm_w: torch.Tensor, eps: float,
+                   cos: torch.Tensor, sin: torch.Tensor, pos: torch.Tensor, slot: torch.Tensor,
+                   page_table: torch.Tensor, cache: Optional[torch.Tensor], n_heads: int, dim: int, rot_dim: int,
+                   rot_dims: int, kv_rank: int, page_shift: int, write_cache: bool = True,
+                   interleaved: bool = True, pdl: bool = False) -> None:
+    """From a token's projected row ``proj`` ([queries: heads x (dim + rot_dim) | from ``c_off``: kv_rank latent,
+    rot_dim key part]): the rotated query parts into ``q_abs`` ([heads x (kv_rank + rot_dim)], behind each
+    head's first kv_rank columns), and the token's cache row [RMS-normed latent * norm_w | rotated key part]
+    at its position.  The first ``rot_dims`` coordinates of a rotated part turn, the rest pass."""
+    _need(proj, "proj", None, 2); _need(q_abs, "q_abs", proj.dtype, 2); _need(norm_w, "norm_w", None, 1)
+    _need(cos, "cos", torch.float32, 2); _need(sin, "sin", torch.float32, 2)
+    _need(pos, "pos", torch.int32, 1); _need(slot, "slot", torch.int32, 1); _need(page_table, "page_table", torch.int32, 2)
+    T = proj.shape[0]
+    if proj.shape[1] < max(n_heads * (dim + rot_dim), c_off + kv_rank + rot_dim) or \
+            q_abs.shape[0] != T or q_abs.shape[1] < n_heads * (kv_rank + rot_dim):
+        raise KernelError("latent_prepare: rows are too narrow")
+    if cos.shape != sin.shape or cos.shape[1] * 2 != rot_dims or not (cos.is_contiguous() and sin.is_contiguous()):
+        raise KernelError("latent_prepare: cos/sin must be [positions, rot_dims/2], contiguous")
+    if norm_w.shape[0] != kv_rank or pos.shape[0] != T or slot.shape[0] != T:
+        raise KernelError("latent_prepare: sizes")
+    if write_cache:
+        _need(cache, "cache", proj.dtype)
+        if not cache.is_contiguous() or cache.shape[-1] != kv_rank + rot_dim:
+            raise KernelError("latent_prepare: the cache entry must be contiguous with rows of kv_rank + rot_dim")
+    _check(_fn("latent_ops", "ssb_latent_prepare")(
+        _ptr(proj), c_int(proj.stride(0)), c_int(c_off), _ptr(q_abs), c_int(q_abs.stride(0)),
+        c_int(dtype_code(proj.dtype)), _ptr(norm_w), c_int(dtype_code(norm_w.dtype)), c_float(eps), _ptr(cos),
+        _ptr(sin), c_int(cos.shape[0]), _ptr(pos), _ptr(slot), _ptr(page_table), c_int(page_table.shape[1]),
+        _ptr(cache), c_int(T), c_int(n_heads), c_int(dim), c_int(rot_dim), c_int(rot_dims), c_int(kv_rank),
+        c_int(page_shift), c_int(1 if write_cache else 0), c_int(1 if interleaved else 0), c_int(1 if pdl else 0),
+        _stream()), "latent_prepare")
+
+
+# ---- linear recurrences ----------------------------------------------------------------
+SCAN_MAX_DIM = 256
+
+
+def gated_linear_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, z: torch.Tensor,
+                      z_bias: torch.Tensor, tau: float, q_scale: float, state: torch.Tensor,
+                      cu_new: torch.Tensor, seq_slot: torch.Tensor, out: torch.Tensor, n_heads: int, dim: int,
+                      vdim: int, pdl: bool = False) -> None:
+    """Per sequence and head, over the sequence's new tokens in order:
+    S = diag(sigmoid(z + z_bias)^(1/tau)) S + k v^T;  out = S^T (q * q_scale), with S [dim, vdim] float32 read
+    from and left in ``state[slot]``.  q, k (heads x dim) and v (heads x vdim) are columns of ``proj``."""
+    _need(proj, "proj", None, 2); _need(z, "z", torch.float32, 2); _need(z_bias, "z_bias", torch.float32, 1)
+    _need(state, "state", torch.float32, 2); _need(out, "out", torch.float32, 2)
+    _need(cu_new, "cu_new", torch.int32, 1); _need(seq_slot, "seq_slot", torch.int32, 1)
+    T, B = proj.shape[0], seq_slot.shape[0]
+    if z.shape[0] != T or out.shape[0] != T or z.shape[1] < n_heads * dim or out.shape[1] < n_heads * vdim \
+            or z_bias.shape[0] != n_heads * dim or cu_new.shape[0] != B + 1:
+        raise KernelError("gated_linear_scan: sizes")
+    if max(q_off, k_off) + n_heads * dim > proj.shape[1] or v_off + n_heads * vdim > proj.shape[1]:
+        raise KernelError("gated_linear_scan: proj rows are too narrow")
+    if state.shape[1] != n_heads * dim * vdim or not state.is_contiguous() or dim > SCAN_MAX_DIM:
+        raise KernelError(f"gated_linear_scan: state rows of heads x dim x vdim, dim up to {SCAN_MAX_DIM}")
+    _check(_fn("recurrence_ops", "ssb_gated_linear_scan")(
+        _ptr(proj), c_int(proj.stride(0)), c_int(dtype_code(proj.dtype)), c_int(q_off), c_int(k_off), c_int(v_off),
+        _ptr(z), c_int(z.stride(0)), _ptr(z_bias), c_float(tau), c_float(q_scale), _ptr(state), _ptr(cu_new),
+        _ptr(seq_slot), _ptr(out), c_int(out.stride(0)), c_int(B), c_int(n_heads), c_int(dim), c_int(vdim),
+        c_int(1 if pdl else 0), _stream()), "gated_linear_scan")
+
+
+def head_norm_gate(o: torch.Tensor, weight: torch.Tensor, eps: float, gate: torch.Tensor, out: torch.Tensor,
+                   n_heads: int, vdim: int, pdl: bool = False) -> None:
+    """out[t, h] = o[t, h] / sqrt(mean(o[t, h]^2) + eps) * weight * silu(gate[t, h]): every head's ``vdim``
+    outputs normalised on their own with one weight vector, then gated.  ``o`` float32."""
+    _need(o, "o", torch.float32, 2); _need(weight, "weight", None, 1); _need(gate, "gate", None, 2)
+    _need(out, "out", gate.dtype, 2)
+    T = o.shape[0]
+    if gate.shape[0] != T or out.shape[0] != T or min(o.shape[1], gate.shape[1], out.shape[1]) < n_heads * vdim \
+            or weight.shape[0] != vdim:
+        raise KernelError("head_norm_gate: sizes")
+    _check(_fn("recurrence_ops", "ssb_head_norm_gate")(
+        _ptr(o), c_int(o.stride(0)), _ptr(weight), c_int(dtype_code(weight.dtype)), c_float(eps), _ptr(gate),
+        c_int(gate.stride(0)), _ptr(out), c_int(out.stride(0)), c_int(dtype_code(out.dtype)), c_int(T),
+        c_int(n_heads), c_int(vdim), c_int(1 if pdl else 0), _stream()), "head_norm_gate")
+
+
+# ---- experts -----------------------------------------------------------------------------
+def route_table(token_ids: torch.Tensor, table: torch.Tensor, n_experts: int, expert_of: torch.Tensor,
+                pair_weight: torch.Tensor, pdl: bool = False) -> None:
+    """expert_of[t, k] = table[token_ids[t], k], pair_weight[t, k] = 1 / top."""
+    _need(token_ids, "token_ids", torch.int32, 1); _need(table, "table", torch.int32, 2)
+    _need(expert_of, "expert_of", torch.int32, 2); _need(pair_weight, "pair_weight", torch.float32, 2)
+    T, top = token_ids.shape[0], table.shape[1]
+    if tuple(expert_of.shape) != (T, top) or tuple(pair_weight.shape) != (T, top) or not (
+            table.is_contiguous() and expert_of.is_contiguous() and pair_weight.is_contiguous()):
+        raise KernelError("route_table: expert_of and pair_weight must be [tokens, top], contiguous")
+    _check(_fn("expert_ops", "ssb_route_table")(
+        _ptr(token_ids), _ptr(table), c_int(table.shape[0]), c_int(top), c_int(n_experts), _ptr(expert_of),
+        _ptr(pair_weight), c_int(T), c_int(1 if pdl else 0), _stream()), "route_table")
+
+
+def expert_tiles_bound(n_pairs: int, n_experts: int, tile_rows: int) -> int:
+    """The most row tiles ``n_pairs`` pairs spread over ``n_experts`` groups can make."""
+    return n_pairs // tile_rows + min(n_experts, n_pairs)
+
+
+def group_by_expert(expert_of: torch.Tensor, n_experts: int, tile_rows: int, offsets: torch.Tensor,
+                    order: torch.Tensor, tile_expert: torch.Tensor, tile_row0: torch.Tensor, meta: torch.Tensor,
+                    pdl: bool = False) -> None:
+    """Sort the (token, choice) pairs by expert: ``order[r]`` is the pair at sorted row r, ``offsets[e]`` the
+    first row of expert e, and (tile_expert, tile_row0)[i < meta[0]] the row tiles of ``tile_rows`` rows."""
+    for t, n in ((expert_of, "expert_of"), (offsets, "offsets"), (order, "order"), (tile_expert, "tile_expert"),
+                 (tile_row0, "tile_row0"), (meta, "meta")):
+        _need(t, n, torch.int32)
+        if not t.is_contiguous():
+            raise KernelError(f"group_by_expert: {n} must be contiguous")
+    P = expert_of.numel()
+    bound = expert_tiles_bound(P, n_experts, tile_rows)
+    if offsets.numel() < n_experts + 1 or order.numel() < P or tile_expert.numel() < bound or tile_row0.numel() < bound:
+        raise KernelError("group_by_expert: outputs are too small")
+    _check(_fn("expert_ops", "ssb_group_by_expert")(
+        _ptr(expert_of), c_int(P), c_int(n_experts), c_int(tile_rows), _ptr(offsets), _ptr(order),
+        _ptr(tile_expert), _ptr(tile_row0), _ptr(meta), c_int(1 if pdl else 0), _stream()), "group_by_expert")
+
+
+def grouped_gemm_plain(a: torch.Tensor, a_index: Optional[torch.Tensor], a_div: int, w: torch.Tensor,
+                       out: torch.Tensor, c_index: Optional[torch.Tensor], offsets: torch.Tensor,
+                       tile_expert: torch.Tensor, tile_row0: torch.Tensor, meta: torch.Tensor, max_tiles: int) -> None:
+    """For sorted row r of expert e: out[c_index[r] or r] = w[e] @ a[a_index[r] // a_div or r]; ``w`` [E, N, K].
+    Tiles of 64 rows (``group_by_expert`` with tile_rows = 64)."""
+    _need(a, "a", None, 2); _need(w, "w", a.dtype, 3); _need(out, "out", None, 2)
+    E, N, K = w.shape
+    if a.shape[1] != K or out.shape[1] != N or not w.is_contiguous():
+        raise KernelError(f"grouped_gemm: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+    _check(_fn("expert_ops", "ssb_grouped_gemm_plain")(
+        _ptr(a), c_int(a.stride(0)), _ptr(a_index), c_int(a_div), _ptr(w), c_int(K), c_longlong(N * K),
+        c_int(dtype_code(a.dtype)), _ptr(out), c_int(out.stride(0)), _ptr(c_index), c_int(dtype_code(out.dtype)),
+        _ptr(offsets), _ptr(tile_expert), _ptr(tile_row0), _ptr(meta), c_int(max_tiles), c_int(N), c_int(K),
+        _stream()), "grouped_gemm_plain")
+
+
+def expert_combine(residual: torch.Tensor, y: torch.Tensor, pair_weight: torch.Tensor, top: int,
+                   pdl: bool = False) -> None:
+    """residual[t] += sum_k pair_weight[t, k] * y[t * top + k], in the order of k."""
+    _need(residual, "residual", torch.float32, 2); _need(y, "y", None, 2); _need(pair_weight, "pair_weight", torch.float32, 2)
+    T, width = residual.shape
+    if tuple(y.shape) != (T * top, width) or tuple(pair_weight.shape) != (T, top) or not pair_weight.is_contiguous():
+        raise KernelError("expert_combine: y [tokens * top, width], pair_weight [tokens, top]")
+    _check(_fn("expert_ops", "ssb_expert_combine")(
+        _ptr(residual), c_int(residual.stride(0)), _ptr(y), c_int(y.stride(0)), c_int(dtype_code(y.dtype)),
+        _ptr(pair_weight), c_int(top), c_int(T), c_int(width), c_int(1 if pdl else 0), _stream()), "expert_combine")
 
 
 # ---- sampling --------------------------------------------------------------------------

@@ -100,8 +100,12 @@ SSB_API int ssb_rmsnorm(const float* x, const int* rows, const void* w, int w_dt
 template <typename TA, typename TC, bool ACCUMULATE>
 __global__ void __launch_bounds__(256)
 gemm_nt_plain_kernel(const TA* __restrict__ A, int lda, const TA* __restrict__ W, int ldw,
-                     TC* __restrict__ C, int ldc, int M, int N, int K) {
+                     TC* __restrict__ C, int ldc, int M, int N, int K,
+                     long long a_batch, long long w_batch, long long c_batch) {
     constexpr int BM = 64, BN = 64, BK = 16;
+    A += (size_t)blockIdx.z * a_batch;        // one product per blockIdx.z (heads of a per-head projection)
+    W += (size_t)blockIdx.z * w_batch;
+    C += (size_t)blockIdx.z * c_batch;
     __shared__ float As[BK][BM + 1];
     __shared__ float Ws[BK][BN + 1];
     const int tid = threadIdx.x;
@@ -167,16 +171,19 @@ gemm_nt_plain_kernel(const TA* __restrict__ A, int lda, const TA* __restrict__ W
     }
 }
 
-SSB_API int ssb_gemm_nt_plain(const void* A, int lda, const void* W, int ldw, int in_dtype, void* C,
-                              int ldc, int out_dtype, int M, int N, int K, int accumulate,
-                              cudaStream_t stream) {
-    if (M <= 0 || N <= 0) return 0;
-    if (K <= 0) return SSB_ERR_BAD_SIZE;
+// ``n_batch`` products of the same sizes whose operands lie ``*_batch`` elements apart (per-head
+// projections: a head's columns of a packed row, a head's own matrix); 1 and zeros: one product
+static int gemm_nt_plain_launch(const void* A, int lda, long long a_batch, const void* W, int ldw,
+                                long long w_batch, int in_dtype, void* C, int ldc, long long c_batch,
+                                int out_dtype, int n_batch, int M, int N, int K, int accumulate,
+                                cudaStream_t stream) {
+    if (M <= 0 || N <= 0 || n_batch <= 0) return 0;
+    if (K <= 0 || n_batch > 65535) return SSB_ERR_BAD_SIZE;
     if (accumulate && out_dtype != SSB_F32) return SSB_ERR_BAD_DTYPE;
-    dim3 grid((N + 63) / 64, (M + 63) / 64);
+    dim3 grid((N + 63) / 64, (M + 63) / 64, n_batch);
 #define SSB_GEMM(TA, TC, ACC) \
     gemm_nt_plain_kernel<TA, TC, ACC><<<grid, 256, 0, stream>>>( \
-        (const TA*)A, lda, (const TA*)W, ldw, (TC*)C, ldc, M, N, K)
+        (const TA*)A, lda, (const TA*)W, ldw, (TC*)C, ldc, M, N, K, a_batch, w_batch, c_batch)
     if (in_dtype == SSB_F32 && out_dtype == SSB_F32) {
         if (accumulate) SSB_GEMM(float, float, true); else SSB_GEMM(float, float, false);
     } else if (in_dtype == SSB_BF16 && out_dtype == SSB_F32) {
@@ -190,6 +197,19 @@ SSB_API int ssb_gemm_nt_plain(const void* A, int lda, const void* W, int ldw, in
     return ssb_launch_status();
 }
 
+SSB_API int ssb_gemm_nt_plain(const void* A, int lda, const void* W, int ldw, int in_dtype, void* C,
+                              int ldc, int out_dtype, int M, int N, int K, int accumulate,
+                              cudaStream_t stream) {
+    return gemm_nt_plain_launch(A, lda, 0, W, ldw, 0, in_dtype, C, ldc, 0, out_dtype, 1, M, N, K, accumulate, stream);
+}
+
+SSB_API int ssb_gemm_nt_plain_batched(const void* A, int lda, long long a_batch, const void* W, int ldw,
+                                      long long w_batch, int in_dtype, void* C, int ldc, long long c_batch,
+                                      int out_dtype, int n_batch, int M, int N, int K, cudaStream_t stream) {
+    return gemm_nt_plain_launch(A, lda, a_batch, W, ldw, w_batch, in_dtype, C, ldc, c_batch, out_dtype, n_batch,
+                                M, N, K, 0, stream);
+}
+
 // ---------------------------------------------------------------------------------------
 // rotary position encoding on q (in place) and k, then k and v into the paged cache
 // qkv row layout: [q heads | k heads | v heads], each head_dim wide
@@ -200,7 +220,8 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, int ld, const float* __r
                                    const int* __restrict__ pos, const int* __restrict__ slot,
                                    const int* __restrict__ page_table, int max_pages,
                                    T* __restrict__ k_cache, T* __restrict__ v_cache, int n_q, int n_kv,
-                                   int head_dim, int rotary_dim, int page_shift, int write_cache) {
+                                   int head_dim, int rotary_dim, int page_shift, int write_cache,
+                                   int interleaved) {
     const int t = blockIdx.x;
     const int s = slot[t];
     if (s < 0) return;                                   // padding row
@@ -211,14 +232,16 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, int ld, const float* __r
     const float* c_row = have_table ? cos_t + (size_t)p * half : nullptr;
     const float* s_row = have_table ? sin_t + (size_t)p * half : nullptr;
     const int n_rot_heads = write_cache ? n_q + n_kv : n_q;
-    // rotate q heads (and k heads), pairs (i, i + half) of the first rotary_dim elements
+    // rotate q heads (and k heads): pairs (i, i + half) of the first rotary_dim elements, or
+    // (interleaved) pairs (2i, 2i + 1)
     for (int e = threadIdx.x; e < n_rot_heads * half; e += blockDim.x) {
         const int h = e / half, i = e % half;
         T* x = row + (size_t)h * head_dim;
+        const int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + half;
         const float c = have_table ? c_row[i] : 1.f, sn = have_table ? s_row[i] : 0.f;
-        const float x1 = ssb_to_float(x[i]), x2 = ssb_to_float(x[i + half]);
-        x[i] = ssb_from_float<T>(x1 * c - x2 * sn);
-        x[i + half] = ssb_from_float<T>(x1 * sn + x2 * c);
+        const float x1 = ssb_to_float(x[ia]), x2 = ssb_to_float(x[ib]);
+        x[ia] = ssb_from_float<T>(x1 * c - x2 * sn);
+        x[ib] = ssb_from_float<T>(x1 * sn + x2 * c);
     }
     if (!write_cache) return;
     __syncthreads();
@@ -236,17 +259,17 @@ SSB_API int ssb_rope_append(void* qkv, int ld, int dtype, const float* cos_t, co
                             int table_positions, const int* pos, const int* slot,
                             const int* page_table, int max_pages, void* k_cache, void* v_cache,
                             int n_tokens, int n_q, int n_kv, int head_dim, int rotary_dim,
-                            int page_shift, int write_cache, cudaStream_t stream) {
+                            int page_shift, int write_cache, int interleaved, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (rotary_dim % 2 || rotary_dim > head_dim || rotary_dim < 0) return SSB_ERR_BAD_SIZE;
     if (dtype == SSB_F32)
         rope_append_kernel<float><<<n_tokens, 256, 0, stream>>>(
             (float*)qkv, ld, cos_t, sin_t, table_positions, pos, slot, page_table, max_pages,
-            (float*)k_cache, (float*)v_cache, n_q, n_kv, head_dim, rotary_dim, page_shift, write_cache);
+            (float*)k_cache, (float*)v_cache, n_q, n_kv, head_dim, rotary_dim, page_shift, write_cache, interleaved);
     else if (dtype == SSB_BF16)
         rope_append_kernel<bf16><<<n_tokens, 256, 0, stream>>>(
             (bf16*)qkv, ld, cos_t, sin_t, table_positions, pos, slot, page_table, max_pages,
-            (bf16*)k_cache, (bf16*)v_cache, n_q, n_kv, head_dim, rotary_dim, page_shift, write_cache);
+            (bf16*)k_cache, (bf16*)v_cache, n_q, n_kv, head_dim, rotary_dim, page_shift, write_cache, interleaved);
     else
         return SSB_ERR_BAD_DTYPE;
     return ssb_launch_status();
@@ -258,7 +281,7 @@ SSB_API int ssb_rope_append(void* qkv, int ld, int dtype, const float* cos_t, co
 // every sum depends on the token's own position and window only.
 // ---------------------------------------------------------------------------------------
 constexpr int ATT_THREADS = 128;
-constexpr int ATT_MAX_HEAD_DIM = 512;
+constexpr int ATT_MAX_HEAD_DIM = 1024;
 
 __device__ __forceinline__ float block_reduce_max(float v, float* red) {
     red[threadIdx.x] = v;
@@ -290,15 +313,15 @@ attention_plain_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k
                        const T* __restrict__ v_cache, const int* __restrict__ pos,
                        const int* __restrict__ slot, const int* __restrict__ page_table, int max_pages,
                        T* __restrict__ out, int ldo, int n_q, int n_kv, int head_dim, int page_shift,
-                       int window, float scale) {
+                       int window, float scale, int v_dim, int v_row, const float* __restrict__ sinks) {
     __shared__ float q_s[ATT_MAX_HEAD_DIM];
     __shared__ float p_s[ATT_THREADS];
     __shared__ float red[ATT_THREADS];
     const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
-    T* o = out + (size_t)t * ldo + (size_t)h * head_dim;
+    T* o = out + (size_t)t * ldo + (size_t)h * v_dim;
     const int s = slot[t];
     if (s < 0) {
-        for (int d = tid; d < head_dim; d += ATT_THREADS) o[d] = ssb_from_float<T>(0.f);
+        for (int d = tid; d < v_dim; d += ATT_THREADS) o[d] = ssb_from_float<T>(0.f);
         return;
     }
     const int p = pos[t];
@@ -333,11 +356,11 @@ attention_plain_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k
 #pragma unroll
         for (int i = 0; i < ATT_MAX_HEAD_DIM / ATT_THREADS; ++i) {
             const int d = tid + i * ATT_THREADS;
-            if (d < head_dim) {
+            if (d < v_dim) {
                 float a = acc[i] * alpha;
                 for (int jj = 0; jj < n_in; ++jj) {
                     const T* vr = v_cache + ssb_cache_row(page_table, max_pages, s, base + jj, page_shift,
-                                                          n_kv, kvh, head_dim);
+                                                          n_kv, kvh, v_row);
                     a = fmaf(p_s[jj], ssb_to_float(vr[d]), a);
                 }
                 acc[i] = a;
@@ -346,10 +369,18 @@ attention_plain_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k
         m = m_new;
         __syncthreads();
     }
+    // a sink: one more term exp(sink) in the denominator, with no key and no value
+    float keep = 1.f;
+    if (sinks != nullptr) {
+        const float sk = sinks[h];
+        const float m_all = fmaxf(m, sk);
+        keep = (m == -INFINITY) ? 0.f : expf(m - m_all);
+        l = l * keep + expf(sk - m_all);
+    }
 #pragma unroll
     for (int i = 0; i < ATT_MAX_HEAD_DIM / ATT_THREADS; ++i) {
         const int d = tid + i * ATT_THREADS;
-        if (d < head_dim) o[d] = ssb_from_float<T>(l > 0.f ? acc[i] / l : 0.f);
+        if (d < v_dim) o[d] = ssb_from_float<T>(l > 0.f ? acc[i] * keep / l : 0.f);
     }
 }
 
@@ -357,18 +388,22 @@ SSB_API int ssb_attention_plain(const void* q, int ldq, int dtype, const void* k
                                 const void* v_cache, const int* pos, const int* slot,
                                 const int* page_table, int max_pages, void* out, int ldo, int n_tokens,
                                 int n_q, int n_kv, int head_dim, int page_shift, int window, float scale,
-                                cudaStream_t stream) {
+                                int v_dim, int v_row, const float* sinks, cudaStream_t stream) {
+    // v_dim: width of a value and of a head's output; v_row: elements between the value rows of
+    // consecutive tokens (values may be the first v_dim elements of the key rows: pass the key
+    // store as v_cache and v_row = head_dim); sinks: one float per query head, or null
     if (n_tokens <= 0) return 0;
     if (head_dim > ATT_MAX_HEAD_DIM || head_dim <= 0 || n_kv <= 0 || n_q % n_kv) return SSB_ERR_BAD_SIZE;
+    if (v_dim <= 0 || v_dim > ATT_MAX_HEAD_DIM || v_row < v_dim) return SSB_ERR_BAD_SIZE;
     dim3 grid(n_tokens, n_q);
     if (dtype == SSB_F32)
         attention_plain_kernel<float><<<grid, ATT_THREADS, 0, stream>>>(
             (const float*)q, ldq, (const float*)k_cache, (const float*)v_cache, pos, slot, page_table,
-            max_pages, (float*)out, ldo, n_q, n_kv, head_dim, page_shift, window, scale);
+            max_pages, (float*)out, ldo, n_q, n_kv, head_dim, page_shift, window, scale, v_dim, v_row, sinks);
     else if (dtype == SSB_BF16)
         attention_plain_kernel<bf16><<<grid, ATT_THREADS, 0, stream>>>(
             (const bf16*)q, ldq, (const bf16*)k_cache, (const bf16*)v_cache, pos, slot, page_table,
-            max_pages, (bf16*)out, ldo, n_q, n_kv, head_dim, page_shift, window, scale);
+            max_pages, (bf16*)out, ldo, n_q, n_kv, head_dim, page_shift, window, scale, v_dim, v_row, sinks);
     else
         return SSB_ERR_BAD_DTYPE;
     return ssb_launch_status();
@@ -423,4 +458,42 @@ SSB_API int ssb_add_into(float* out, const void* x, int x_dtype, long long n, cu
     else if (x_dtype == SSB_BF16) add_into_kernel<bf16><<<blocks, 256, 0, stream>>>(out, (const bf16*)x, (size_t)n);
     else return SSB_ERR_BAD_DTYPE;
     return ssb_launch_status();
+}
+
+// ---------------------------------------------------------------------------------------
+// x (float32) *= s
+// ---------------------------------------------------------------------------------------
+__global__ void scale_kernel(float* __restrict__ x, float s, size_t n) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] *= s;
+}
+
+SSB_API int ssb_scale(float* x, float s, long long n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    scale_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(x, s, (size_t)n);
+    return ssb_launch_status();
+}
+
+// ---------------------------------------------------------------------------------------
+// out[e] = sum_{j < n_terms} w[j] * streams[j * stride + e]: a weighted sum of the first n_terms of a
+// stack of float32 streams, added in the order of j
+// ---------------------------------------------------------------------------------------
+__global__ void stream_mix_kernel(const float* __restrict__ streams, size_t stride, const float* __restrict__ w,
+                                  int n_terms, float* __restrict__ out, size_t n) {
+    ssb_pdl_launch_dependents();
+    ssb_pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float acc = 0.f;
+    for (int j = 0; j < n_terms; ++j) acc = fmaf(w[j], streams[(size_t)j * stride + i], acc);
+    out[i] = acc;
+}
+
+SSB_API int ssb_stream_mix(const float* streams, long long stride, const float* w, int n_terms, float* out,
+                           long long n, int pdl, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (n_terms <= 0) return SSB_ERR_BAD_SIZE;
+    const int rc = ssb_launch(stream_mix_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, pdl != 0,
+                              streams, (size_t)stride, w, n_terms, out, (size_t)n);
+    return rc ? rc : ssb_launch_status();
 }

@@ -59,6 +59,8 @@ class StepContext:
     kernels: Any
     dtype: torch.dtype
     stage: str = ""            # the part that is running ("embed", "mixer", "feed_forward", "head"): for stage timings
+    streams: Any = None        # what a block arrangement keeps from layer to layer within one step (the stack of
+                               # earlier layers' results for a weighted sum over depth)
 
 
 class DecodeGraph:
@@ -212,10 +214,13 @@ class Model:
         self.blocks = []
         for b in spec.blocks:
             mixer = part(MIXERS, "mixer", b.mixer)
-            ff = part(FEED_FORWARDS, "feed-forward", b.feed_forward)
-            n1, n2 = part(NORMS, "norm", b.mixer_norm), part(NORMS, "norm", b.feed_forward_norm)
+            ff = part(FEED_FORWARDS, "feed-forward", b.feed_forward) if b.feed_forward else None
+            n1 = part(NORMS, "norm", b.mixer_norm)
+            n2 = part(NORMS, "norm", b.feed_forward_norm) if b.feed_forward_norm else None
             pos = part(POSITION_ENCODINGS, "position encoding", b.position) if b.position else None
-            self.blocks.append(lookup(BLOCKS, b.kind, "block")(mixer, ff, n1, n2, pos))
+            # an arrangement with constants or tensors of its own gets them like any other part
+            own = {"params": b.params, "weights": b.weights, "build": build} if (b.params or b.weights) else {}
+            self.blocks.append(lookup(BLOCKS, b.kind, "block")(mixer, ff, n1, n2, pos, **own))
         self.final_norm = part(NORMS, "norm", spec.final_norm)
         self.head = part(HEADS, "head", spec.head)
         weights.forget()
@@ -277,13 +282,15 @@ class Model:
         error unless ``allow_unexpected_tensors`` turns it into a warning."""
         config = load_config(model_dir)
         store = WeightStore.from_dir(model_dir)
+        if hasattr(config, "with_shapes"):        # sizes that only the stored tensors' shapes give
+            config = config.with_shapes(store)
         store.check(config.tensor_shapes(), ignorable=getattr(config, "ignorable_tensor", None),
-                    allow_unexpected=allow_unexpected_tensors)
+                    allow_unexpected=allow_unexpected_tensors, integer=getattr(config, "integer_tensor", None))
         return Model(spec_from_config(config), store, config=config, **kw)
 
     @staticmethod
     def from_config(config, store: WeightStore, **kw) -> "Model":
-        store.check(config.tensor_shapes())
+        store.check(config.tensor_shapes(), integer=getattr(config, "integer_tensor", None))
         return Model(spec_from_config(config), store, config=config, **kw)
 
     @property
@@ -435,11 +442,15 @@ class Model:
         if self.nvtx:                                       # a named range per stop of the schedule, for timelines
             for i, stop in enumerate(self.spec.schedule):
                 torch.cuda.nvtx.range_push(f"stop {i} layer {stop.layer}")
-                self.blocks[stop.layer].forward(ctx, residual, stop.cache, stop.writes_cache)
+                moved = self.blocks[stop.layer].forward(ctx, residual, stop.cache, stop.writes_cache)
+                residual = residual if moved is None else moved
                 torch.cuda.nvtx.range_pop()
         else:
+            # a block updates the stream in place, or returns the tensor that holds it from now on
             for stop in self.spec.schedule:
-                self.blocks[stop.layer].forward(ctx, residual, stop.cache, stop.writes_cache)
+                moved = self.blocks[stop.layer].forward(ctx, residual, stop.cache, stop.writes_cache)
+                if moved is not None:
+                    residual = moved
         if batch.n_want == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
         ctx.stage = "head"

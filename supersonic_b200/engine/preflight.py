@@ -68,6 +68,7 @@ def weight_bytes(spec, store, dtype: torch.dtype) -> int:
     (a tied head) is counted once."""
     item = torch.empty((), dtype=dtype).element_size()
     names = {n for p in _part_specs(spec) for n in p.weights.values()}
+    names |= {n for b in spec.blocks for n in b.weights.values()}
     total = 0
     for n in names:
         if n not in store:
@@ -101,10 +102,15 @@ def workspace_bytes(spec, dtype: torch.dtype, step_tokens: int, decode_rows: int
     for b in spec.blocks:
         here = 0
         for ps, table, what in ((b.mixer, MIXERS, "mixer"), (b.feed_forward, FEED_FORWARDS, "feed-forward")):
+            if ps is None:
+                continue
             hook = getattr(lookup(table, ps.kind, what), "activation_elements", None)
             here = max(here, int(hook(ps.params)) if hook is not None else 4 * spec.hidden_size)
         widest = max(widest, here)
-    per_token = 4 * spec.hidden_size + item * (2 * spec.hidden_size + widest)
+    # an arrangement that keeps every layer's result within a step says how many float32 streams it holds
+    streams = max([int(b.params.get("depth_average", {}).get("layers", 0)) + 2 if b.params.get("depth_average") else 1
+                   for b in spec.blocks] + [1])
+    per_token = 4 * spec.hidden_size * streams + item * (2 * spec.hidden_size + widest)
     return step_tokens * per_token + 2 * decode_rows * spec.vocab_size * 4
 
 

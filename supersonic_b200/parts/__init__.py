@@ -1,5 +1,6 @@
 """Parts a model is put together from; importing this package registers the built-in ones."""
-from . import attention, block, embedding, feed_forward, head, norm, rotary  # noqa: F401
+from . import (attention, block, embedding, experts, feed_forward, head, latent_attention,  # noqa: F401
+               linear_attention, norm, rotary)
 from .registry import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS,
                        POSITION_ENCODINGS, BuildContext, WeightAccess, lookup, register_block,
                        register_embedding, register_feed_forward, register_head, register_mixer,

@@ -1,6 +1,10 @@
 """Block arrangements.  ``pre_norm``: h += mixer(norm(h)); h += feed_forward(norm(h)),
-the residual stream kept and summed in float32 (crates/runner/src/prefill_engine.rs:1116-1222)."""
+the residual stream kept and summed in float32 (crates/runner/src/prefill_engine.rs:1116-1222).
+``parallel``: h += mixer(n) + feed_forward(n) with the one n = norm(h), optionally followed by a
+learned weighted sum over the results of all layers so far."""
 from __future__ import annotations
+
+import torch
 
 from ..csrc.kernel_sets import NormedInput
 from .registry import register_block
@@ -26,6 +30,60 @@ class PreNormBlock:
         x = NormedInput(ctx, residual, self.mixer_norm)
         ctx.stage = "mixer"           # names the running part for stage timings; nothing depends on it
         self.mixer.forward(ctx, self._give(x, self.mixer), residual, cache_id, writes_cache, self.position)
+        if self.feed_forward is None:
+            return
         x2 = NormedInput(ctx, residual, self.feed_forward_norm)
         ctx.stage = "feed_forward"
         self.feed_forward.forward(ctx, self._give(x2, self.feed_forward), residual)
+
+
+@register_block("parallel")
+class ParallelBlock:
+    """x <- x + mixer(n) + feed_forward(n), n = norm(x): one norm, read by both sublayers (the
+    feed-forward may be absent).
+
+    ``params["depth_average"] = {"index": i, "layers": L}`` adds a weighted sum over depth: with X_0
+    the stream that enters the first layer and X_(j+1) the result of layer j, the stream that leaves
+    layer i is sum_{j <= i+1} w[j] X_j, with the layer's own weights ``depth_weights`` (i + 2 numbers).
+    The results of a step's layers are kept in one float32 stack ``ctx.streams`` [L + 2, T, width]: plane
+    i + 1 holds the stream entering layer i, the sublayers add into it in place (which makes it X_(i+1)),
+    and the weighted sum is written into plane i + 2, which the block returns as the stream from then on.
+    """
+
+    def __init__(self, mixer, feed_forward, mixer_norm, feed_forward_norm, position, params=None,
+                 weights=None, build=None):
+        if feed_forward_norm is not None:
+            raise ValueError("a parallel block has one norm")
+        self.mixer, self.feed_forward, self.mixer_norm, self.position = mixer, feed_forward, mixer_norm, position
+        self.depth = (params or {}).get("depth_average")
+        if self.depth is not None:
+            self.index, self.layers = int(self.depth["index"]), int(self.depth["layers"])
+            w = build.weights.stored(weights["depth_weights"]).float().contiguous()
+            if tuple(w.shape) != (self.index + 2,):
+                raise ValueError(f"{weights['depth_weights']} has shape {tuple(w.shape)}, expected ({self.index + 2},)")
+            self.depth_weights = w
+            self.one = torch.ones(1, dtype=torch.float32, device=build.device)
+
+    _give = staticmethod(PreNormBlock._give)
+
+    def forward(self, ctx, residual, cache_id, writes_cache):
+        if self.depth is not None:
+            if self.index == 0:
+                T, width = residual.shape
+                ctx.streams = torch.empty((self.layers + 2, T, width), dtype=torch.float32, device=residual.device)
+                ctx.kernels.stream_mix(residual.unsqueeze(0), self.one, 1, ctx.streams[0])
+                ctx.kernels.stream_mix(residual.unsqueeze(0), self.one, 1, ctx.streams[1])
+            elif ctx.streams is None:
+                raise RuntimeError("a depth-averaging layer ran before the first one of its step")
+            residual = ctx.streams[self.index + 1]
+        x = NormedInput(ctx, residual, self.mixer_norm)
+        ctx.stage = "mixer"
+        self.mixer.forward(ctx, self._give(x, self.mixer), residual, cache_id, writes_cache, self.position)
+        if self.feed_forward is not None:
+            ctx.stage = "feed_forward"
+            self.feed_forward.forward(ctx, self._give(x, self.feed_forward), residual)
+        if self.depth is None:
+            return None
+        out = ctx.streams[self.index + 2]
+        ctx.kernels.stream_mix(ctx.streams, self.depth_weights, self.index + 2, out)
+        return out

@@ -1,0 +1,120 @@
+"""Feed-forward experts: each token runs ``top`` of ``n_experts`` small gated feed-forwards and adds
+their weighted outputs; an optional shared expert runs for every token and is added too.
+
+An expert is down( silu(gate(x)) * up(x) ) without biases.  Which experts a token uses, and with
+what weights, is the router's business; routers are registered by name:
+
+* ``table``: no learned router at all.  An integer table [vocab, top] gives every token id its
+  experts (the entries of a row differ); each has weight 1 / top.
+
+The step's (token, choice) pairs are sorted by expert on the device, the experts' matrix
+products run group by group from that order, and a token's outputs are summed in the order of
+its choices, so nothing depends on what else is in the step and the launch sizes depend on the
+number of tokens alone (the step can be captured in a graph).
+"""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from ..csrc.kernel_sets import as_tensor
+from .registry import BuildContext, register_feed_forward
+
+ROUTERS: Dict[str, type] = {}
+
+
+def register_router(name: str):
+    def deco(cls):
+        ROUTERS[name] = cls
+        return cls
+    return deco
+
+
+@register_router("table")
+class TableRouter:
+    """params: ``vocab_size``; weights: ``table`` [vocab, top] int32.
+
+    Interface of a router: ``route(ctx, x, expert_of, pair_weight)`` fills the int32 ``expert_of`` and the
+    float32 ``pair_weight`` (both [tokens, top]) for the step's tokens, whose normed activations are ``x``."""
+
+    def __init__(self, params, weights, build: BuildContext, n_experts: int, top: int):
+        self.n_experts, self.top = n_experts, top
+        table = build.weights.stored(weights["table"])
+        if table.dtype != torch.int32 or tuple(table.shape) != (int(params["vocab_size"]), top):
+            raise ValueError(f"{weights['table']}: expected int32 [{params['vocab_size']}, {top}], "
+                             f"found {table.dtype} {tuple(table.shape)}")
+        lo, hi = int(table.min()), int(table.max())
+        if lo < 0 or hi >= n_experts:
+            raise ValueError(f"{weights['table']} names experts {lo}..{hi}; there are {n_experts}")
+        self.table = table.contiguous()
+
+    def route(self, ctx, x, expert_of, pair_weight):
+        ctx.kernels.route_table(ctx.batch.token_ids, self.table, self.n_experts, expert_of, pair_weight)
+
+
+@register_feed_forward("experts")
+class Experts:
+    """params: ``hidden_size``, ``n_experts``, ``top``, ``expert_size``, ``router`` ({"kind": ..., its own
+    parameters}), ``shared`` (None or {"intermediate_size": ...}); weights: ``gate.<e>``, ``up.<e>``,
+    ``down.<e>`` for every expert e, the router's own, and ``shared.gate`` / ``shared.up`` / ``shared.down``."""
+
+    takes_lazy_input = True
+
+    def __init__(self, params, weights, build: BuildContext):
+        self.hidden, self.E = int(params["hidden_size"]), int(params["n_experts"])
+        self.top, self.inter = int(params["top"]), int(params["expert_size"])
+        w, dt = build.weights, build.dtype
+        first, second = [], []
+        for e in range(self.E):
+            gate, up, down = (w.as_dtype(weights[f"{r}.{e}"], dt) for r in ("gate", "up", "down"))
+            for name, t, want in ((f"gate.{e}", gate, (self.inter, self.hidden)), (f"up.{e}", up, (self.inter, self.hidden)),
+                                  (f"down.{e}", down, (self.hidden, self.inter))):
+                if tuple(t.shape) != want:
+                    raise ValueError(f"{weights[name]} has shape {tuple(t.shape)}, expected {want}")
+            first.append(torch.cat([gate, up], dim=0))
+            second.append(down)
+        self.w_gate_up = torch.stack(first).contiguous()       # [E, 2 * inter, hidden]: gate rows, then up rows
+        self.w_down = torch.stack(second).contiguous()         # [E, hidden, inter]
+        router = dict(params["router"])
+        if router.get("kind") not in ROUTERS:
+            raise KeyError(f"unknown router {router.get('kind')!r}; registered: {sorted(ROUTERS)}")
+        self.router = ROUTERS[router["kind"]](router, weights, build, self.E, self.top)
+        self.shared = None
+        if params.get("shared"):
+            from .feed_forward import SwiGLU
+            self.shared = SwiGLU({"hidden_size": self.hidden, "intermediate_size": int(params["shared"]["intermediate_size"])},
+                                 {r: weights[f"shared.{r}"] for r in ("gate", "up", "down")}, build)
+        self.dtype = dt
+
+    @staticmethod
+    def activation_elements(params) -> int:
+        """Elements per token while the part runs: per choice gate, up, their product and the expert's output
+        (float32: counted twice); the shared expert's rows."""
+        shared = 3 * int(params["shared"]["intermediate_size"]) if params.get("shared") else 0
+        return int(params["top"]) * (3 * int(params["expert_size"]) + 2 * int(params["hidden_size"])) + shared
+
+    def forward(self, ctx, x, residual):
+        T, dev, top = residual.shape[0], residual.device, self.top
+        xt = as_tensor(x)
+        P = T * top
+        expert_of = torch.empty((T, top), dtype=torch.int32, device=dev)
+        pair_weight = torch.empty((T, top), dtype=torch.float32, device=dev)
+        self.router.route(ctx, xt, expert_of, pair_weight)
+        tile_rows = ctx.kernels.expert_tile_rows
+        max_tiles = P // tile_rows + min(self.E, P)
+        ints = torch.empty(self.E + 1 + P + 2 * max_tiles + 1, dtype=torch.int32, device=dev)
+        groups = {"tile_rows": tile_rows, "max_tiles": max_tiles, "offsets": ints[: self.E + 1],
+                  "order": ints[self.E + 1: self.E + 1 + P],
+                  "tile_expert": ints[self.E + 1 + P: self.E + 1 + P + max_tiles],
+                  "tile_row0": ints[self.E + 1 + P + max_tiles: self.E + 1 + P + 2 * max_tiles], "meta": ints[-1:]}
+        ctx.kernels.group_by_expert(expert_of, self.E, groups)
+        gate_up = torch.empty((P, 2 * self.inter), dtype=self.dtype, device=dev)
+        ctx.kernels.grouped_linear(xt, True, top, self.w_gate_up, gate_up, False, groups)
+        z = torch.empty((P, self.inter), dtype=self.dtype, device=dev)
+        ctx.kernels.swiglu(gate_up, z)
+        y = torch.empty((P, self.hidden), dtype=torch.float32, device=dev)
+        ctx.kernels.grouped_linear(z, False, top, self.w_down, y, True, groups)
+        ctx.kernels.expert_combine(residual, y, pair_weight, top)
+        if self.shared is not None:
+            self.shared.forward(ctx, x, residual)

@@ -10,10 +10,12 @@ from .registry import BuildContext, register_head
 
 @register_head("linear_head")
 class LinearHead:
-    """params: ``vocab_size``, ``hidden_size``; weights: ``weight`` [vocab, hidden]."""
+    """params: ``vocab_size``, ``hidden_size``, ``scale`` (optional: the logits are multiplied by it);
+    weights: ``weight`` [vocab, hidden]."""
 
     def __init__(self, params, weights, build: BuildContext):
         self.vocab, self.hidden = int(params["vocab_size"]), int(params["hidden_size"])
+        self.scale = float(params.get("scale", 1.0))
         self.weight = build.weights.as_dtype(weights["weight"], build.dtype, share=True)
         if tuple(self.weight.shape) != (self.vocab, self.hidden):
             raise ValueError(f"{weights['weight']} has shape {tuple(self.weight.shape)}, "
@@ -23,4 +25,6 @@ class LinearHead:
         logits = torch.empty((normed_rows.shape[0], self.vocab), dtype=torch.float32,
                              device=normed_rows.device)
         ctx.kernels.linear(normed_rows, self.weight, logits)
+        if self.scale != 1.0:
+            ctx.kernels.scale_(logits, self.scale)
         return logits

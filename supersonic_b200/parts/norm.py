@@ -33,3 +33,22 @@ class RMSNorm:
         out = torch.empty((n, self.size), dtype=self.dtype, device=x.device)
         ctx.kernels.rmsnorm(x, self.weight, self.eps, out, rows)
         return out
+
+
+@register_norm("rmsnorm_scalar")
+class ScalarRMSNorm(RMSNorm):
+    """y = x * rsqrt(mean(x^2) + eps) * g with one gain g for all coordinates.
+
+    params: ``size``, ``eps``; weights: ``weight``, a tensor of a single number.  The gain is spread
+    over a vector when the part is built, so every kernel that takes ``rmsnorm`` (also those that
+    fold the norm into a matrix product) takes this norm unchanged.
+    """
+
+    def __init__(self, params, weights, build: BuildContext):
+        self.size, self.eps = int(params["size"]), float(params["eps"])
+        g = build.weights.stored(weights["weight"])
+        if g.numel() != 1:
+            raise ValueError(f"{weights['weight']} has shape {tuple(g.shape)}, expected a single number")
+        g = g.reshape(1).expand(self.size).contiguous()
+        self.weight = g.float() if build.dtype == torch.float32 else g
+        self.dtype = build.dtype

@@ -32,7 +32,8 @@ def scaled_inverse_frequencies(rotary_dim: int, theta: float, scaling: Optional[
 
 @register_position_encoding("rotary")
 class Rotary:
-    """params: ``head_dim``, ``rotary_dim``, ``theta``, ``max_positions``, ``scaling``.
+    """params: ``head_dim``, ``rotary_dim``, ``theta``, ``max_positions``, ``scaling``, ``pairing``
+    (``"halves"``: coordinate i turns with i + rotary_dim/2, the default; ``"interleaved"``: 2i with 2i + 1).
 
     Interface of a position encoding: ``encode_and_append(ctx, qkv, kv, n_q, n_kv, write)``
     rotates the queries (and keys) of the packed ``qkv`` rows in place by each
@@ -44,6 +45,10 @@ class Rotary:
         self.rotary_dim = int(params.get("rotary_dim", self.head_dim))
         if self.rotary_dim % 2 or self.rotary_dim > self.head_dim:
             raise ValueError(f"rotary_dim {self.rotary_dim} must be even and <= head_dim {self.head_dim}")
+        pairing = params.get("pairing", "halves")
+        if pairing not in ("halves", "interleaved"):
+            raise ValueError(f"rotary pairing {pairing!r} is not known ('halves' or 'interleaved')")
+        self.interleaved = pairing == "interleaved"
         n_pos = min(int(params["max_positions"]), int(build.max_positions))
         self.max_positions = n_pos
         inv = scaled_inverse_frequencies(self.rotary_dim, float(params["theta"]), params.get("scaling"))
@@ -66,7 +71,7 @@ class Rotary:
         k_cache, v_cache, table, group = kv
         from ..cache import PAGE_SHIFT
         ctx.kernels.rope_append(qkv, self.cos, self.sin, ctx.batch, table, k_cache, v_cache, n_q, n_kv,
-                                self.head_dim, self.rotary_dim, PAGE_SHIFT, write_cache)
+                                self.head_dim, self.rotary_dim, PAGE_SHIFT, write_cache, self.interleaved)
 
 
 @register_position_encoding("none")

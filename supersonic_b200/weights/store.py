@@ -106,12 +106,14 @@ class WeightStore:
         t = self._tensors[name]
         return t[0].dtype(t[1]) if isinstance(t, tuple) else t.dtype
 
-    def check(self, expected: Dict[str, List[int]], ignorable=None, allow_unexpected: bool = False) -> None:
+    def check(self, expected: Dict[str, List[int]], ignorable=None, allow_unexpected: bool = False,
+              integer=None) -> None:
         """Raise one :class:`WeightError` listing every mismatch with ``expected``.  ``ignorable(name)``
         names stored tensors that are no parameters (buffers some exporters write, such as
         ``rotary_emb.inv_freq``): they are passed over.  ``allow_unexpected``: other unexpected
         tensors are reported with a warning instead of the error (the reference never looks at
-        tensors it does not ask for: crates/qwen35/src/loader.rs:142-159)."""
+        tensors it does not ask for: crates/qwen35/src/loader.rs:142-159).  ``integer(name)`` names the
+        tensors that are integer tables: those must be stored as integers, all others in floating point."""
         missing = [n for n in expected if n not in self._tensors]
         unexpected = [n for n in self._tensors if n not in expected and not (ignorable and ignorable(n))]
         if unexpected and allow_unexpected:
@@ -126,7 +128,8 @@ class WeightStore:
                 if list(got) != list(want):
                     wrong_shape.append((n, list(want), list(got)))
                 dt = self.stored_dtype(n)
-                if dt not in (torch.bfloat16, torch.float16, torch.float32):
+                floating = dt in (torch.bfloat16, torch.float16, torch.float32)
+                if floating == bool(integer and integer(n)):
                     wrong_dtype.append((n, str(dt)))
         if missing or unexpected or wrong_shape or wrong_dtype:
             raise WeightError(self.where, missing, unexpected, wrong_shape, wrong_dtype)
@@ -152,6 +155,11 @@ def random_tensor(config, seed: int, name: str, device: str = "cpu", std: float 
     """One seeded tensor by name, in bfloat16: matrices and embeddings N(0, std), norm weights
     1 + N(0, norm_jitter).  Its values depend on (seed, name, element index) alone: the same on the
     host and on the device, whole or in pieces (see ``random_fill``)."""
+    special = getattr(config, "special_random_tensor", None)
+    if special is not None:
+        t = special(name, seed, device, std)
+        if t is not None:
+            return t
     shape = config.tensor_shapes()[name]
     is_norm = getattr(config, "is_norm_tensor", lambda n: len(shape) == 1)
     if is_norm(name):
@@ -178,7 +186,8 @@ class RandomWeightStore(WeightStore):
         return list(self._shapes[name])
 
     def stored_dtype(self, name: str) -> torch.dtype:
-        return torch.bfloat16
+        integer = getattr(self._args[0], "integer_tensor", None)
+        return torch.int32 if integer and integer(name) else torch.bfloat16
 
     def get(self, name: str, device: Optional[torch.device] = None) -> torch.Tensor:
         if name not in self._shapes:
@@ -202,7 +211,8 @@ def write_model_folder(config, seed: int, model_dir: str, std: float = 0.02,
     with open(os.path.join(model_dir, "config.json"), "w", encoding="utf-8") as f:
         json.dump(config.to_dict(), f, indent=2)
         f.write("\n")
-    entries = [(n, torch.bfloat16, list(s)) for n, s in config.tensor_shapes().items()]
+    integer = getattr(config, "integer_tensor", lambda n: False)
+    entries = [(n, torch.int32 if integer(n) else torch.bfloat16, list(s)) for n, s in config.tensor_shapes().items()]
     write_safetensors(os.path.join(model_dir, "model.safetensors"), entries,
                       random_tensors(config, seed, "cpu", std, norm_jitter),
                       metadata={"format": "pt", "seed": str(seed)})
