@@ -68,7 +68,7 @@ def fill_host(seed: int, name: str, shape: Sequence[int], mean: float, std: floa
         n = min(_CHUNK, count - first)
         v = (np.float64(mean) + np.float64(std) * _normals(key, first, n)).astype(np.float32)
         out[first:first + n] = torch.from_numpy(v).to(dtype)        # round to nearest even
-    return out.view(*shape)
+    return out.view(tuple(shape))          # () for a tensor of a single number
 
 
 def fill_device(seed: int, name: str, shape: Sequence[int], mean: float, std: float, device,

@@ -124,5 +124,5 @@ def write_safetensors(path: str, entries: List[Tuple[str, torch.dtype, List[int]
                 raise SafetensorsError(f"write {path}: expected {name} {dtype} {shape}, got "
                                        f"{got_name} {t.dtype} {list(t.shape)}")
             t = t.detach().contiguous().cpu()
-            f.write(t.view(torch.uint8).numpy().tobytes() if t.numel() else b"")
+            f.write(t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b"")
     os.replace(tmp, path)

@@ -42,8 +42,9 @@ def rotate_interleaved(v, pos, base, dims):
     return out
 
 
-def latent_attention(h, w, p, m, eps, pos=None):
-    """h [T, width]; ``p`` the tensor prefix ('l0.mix'), ``m`` the mixer's sizes."""
+def latent_attention(h, w, p, m, eps, pos=None, window=None, use_sink=True):
+    """h [T, width]; ``p`` the tensor prefix ('l0.mix'), ``m`` the mixer's sizes.  ``window``: a query
+    sees the last ``window`` keys only (its own included)."""
     T = h.shape[0]
     H, d, r, dv, rank = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
     pos = torch.arange(T) if pos is None else pos
@@ -61,10 +62,12 @@ def latent_attention(h, w, p, m, eps, pos=None):
     out = torch.zeros(T, H, dv, dtype=F)
     for t in range(T):
         for hd in range(H):
-            s = (k_plain[: t + 1, hd] @ q_plain[t, hd] + k_rot[: t + 1] @ q_rot[t, hd]) * m["scale"]
-            top = max(float(s.max()), float(sink[hd]))
+            lo = 0 if window is None else max(0, t - window + 1)
+            s = (k_plain[lo: t + 1, hd] @ q_plain[t, hd] + k_rot[lo: t + 1] @ q_rot[t, hd]) * m["scale"]
+            sk = float(sink[hd]) if use_sink else -math.inf
+            top = max(float(s.max()), sk)
             e = torch.exp(s - top)
-            out[t, hd] = (e[:, None] * v[: t + 1, hd]).sum(0) / (e.sum() + math.exp(float(sink[hd]) - top))
+            out[t, hd] = (e[:, None] * v[lo: t + 1, hd]).sum(0) / (e.sum() + math.exp(sk - top))
     return out.reshape(T, H * dv) @ w[p + ".o"].to(F).T
 
 

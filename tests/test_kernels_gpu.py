@@ -361,11 +361,11 @@ def test_kernels_refuse_what_they_cannot_do():
         ops().gemm_nt_plain(torch.zeros(2, 4, device=DEV, dtype=torch.float16),
                             torch.zeros(3, 4, device=DEV, dtype=torch.float16), torch.zeros(2, 3, device=DEV))
     with pytest.raises(KernelError, match="head_dim"):
-        ops().attention_plain(torch.zeros(1, 1024, device=DEV), torch.zeros(1, 1, 64, 1024, device=DEV),
-                              torch.zeros(1, 1, 64, 1024, device=DEV), torch.zeros(1, dtype=torch.int32, device=DEV),
+        ops().attention_plain(torch.zeros(1, 2048, device=DEV), torch.zeros(1, 1, 64, 2048, device=DEV),
+                              torch.zeros(1, 1, 64, 2048, device=DEV), torch.zeros(1, dtype=torch.int32, device=DEV),
                               torch.zeros(1, dtype=torch.int32, device=DEV),
-                              torch.zeros(1, 1, dtype=torch.int32, device=DEV), torch.zeros(1, 1024, device=DEV),
-                              1, 1, 1024, 6, None, 1.0)
+                              torch.zeros(1, 1, dtype=torch.int32, device=DEV), torch.zeros(1, 2048, device=DEV),
+                              1, 1, 2048, 6, None, 1.0)
 
 
 # ---- decode kernels -----------------------------------------------------------------------
