@@ -1,0 +1,190 @@
+// Many small matrix products in one launch, on the tensor cores (mma.sync m16n8k16, bfloat16 in,
+// float32 accumulation): one matrix per head (C[t, h] = W_h A[t, h]) or one per expert over the rows
+// that a device-side grouping assigned to it.
+//
+// A work tile is 64 rows x 64 output columns of one matrix.  Which matrix and which rows comes from
+// blockIdx.z and blockIdx.y (per-head form), or from the tile list that the grouping kernel wrote
+// (per-expert form: a block whose index is beyond the list's length returns).  Rows of A may be
+// gathered through an index (a_index[r] / a_div) and rows of C scattered through one, so that
+// tokens need not be copied into expert order.  The K range is walked 32 columns a stage through a
+// two-stage cp.async ring.  Epilogues: store (bfloat16 or float32), or SwiGLU: the matrix is
+// [gate rows; up rows] and the tile computes both halves for its columns and stores
+// silu(gate) * up.
+#include "mma_helpers.cuh"
+#include <math.h>
+
+typedef __nv_bfloat16 bf16;
+
+constexpr int BG_BM = 64, BG_BN = 64, BG_BK = 32;
+constexpr int BG_LD = BG_BK + 8;                 // padded row of a stage in elements: 80 bytes, conflict-free ldmatrix
+constexpr int BG_THREADS = 128;
+
+struct BgArgs {
+    const bf16* A; int lda; long long a_batch; const int* a_index; int a_div;
+    const bf16* W; int ldw; long long w_batch;
+    void* C; int ldc; long long c_batch; const int* c_index;
+    const int* offsets; const int* tile_expert; const int* tile_row0; const int* meta;   // grouped form, else null
+    int M, N, K;                                  // M: rows (per-head form); N: output columns; K
+    int up_row0;                                  // SwiGLU: first row of the up half in a matrix
+};
+
+template <bool SWIGLU, typename TC>
+__global__ void __launch_bounds__(BG_THREADS)
+batched_gemm_kernel(const BgArgs g) {
+    __shared__ __align__(16) bf16 a_s[2][BG_BM * BG_LD];
+    __shared__ __align__(16) bf16 w_s[2][(SWIGLU ? 2 : 1) * BG_BN * BG_LD];
+    __shared__ int a_rows[BG_BM];
+    ssb_pdl_launch_dependents();
+    ssb_pdl_wait();
+    int e, r0, r_end;
+    if (g.meta != nullptr) {
+        if ((int)blockIdx.y >= g.meta[0]) return;
+        e = g.tile_expert[blockIdx.y];
+        r0 = g.tile_row0[blockIdx.y];
+        r_end = min(g.offsets[e + 1], r0 + BG_BM);
+    } else {
+        e = blockIdx.z;
+        r0 = blockIdx.y * BG_BM;
+        r_end = min(g.M, r0 + BG_BM);
+    }
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n0 = blockIdx.x * BG_BN;
+    const bf16* A = g.A + (size_t)e * g.a_batch;
+    const bf16* W = g.W + (size_t)e * g.w_batch;
+    if (tid < BG_BM) {
+        const int r = r0 + tid;
+        a_rows[tid] = r < r_end ? (g.a_index ? g.a_index[r] / g.a_div : r) : -1;
+    }
+    __syncthreads();
+    const int K = g.K, N = g.N;
+    auto load_stage = [&](int k0, int stage) {
+        // 64 rows x 4 chunks of 8 elements for A, the same for W (twice for SwiGLU)
+        for (int c = tid; c < BG_BM * 4; c += BG_THREADS) {
+            const int r = c >> 2, ch = c & 3, k = k0 + ch * 8;
+            bf16* dst = &a_s[stage][r * BG_LD + ch * 8];
+            const int m = a_rows[r];
+            if (m >= 0 && k < K) cp_async16((uint32_t)__cvta_generic_to_shared(dst), A + (size_t)m * g.lda + k);
+            else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+        }
+        for (int c = tid; c < (SWIGLU ? 2 : 1) * BG_BN * 4; c += BG_THREADS) {
+            const int r = c >> 2, ch = c & 3, k = k0 + ch * 8;
+            bf16* dst = &w_s[stage][r * BG_LD + ch * 8];
+            const int half = r / BG_BN, n = n0 + r % BG_BN;
+            if (n < N && k < K) cp_async16((uint32_t)__cvta_generic_to_shared(dst),
+                                           W + (size_t)(n + half * g.up_row0) * g.ldw + k);
+            else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+        }
+        cp_async_commit();
+    };
+    // warp w: rows (w & 1) * 32 .. + 31, columns (w >> 1) * 32 .. + 31
+    const int wm = (warp & 1) * 32, wn = (warp >> 1) * 32;
+    float acc[SWIGLU ? 2 : 1][2][4][4];
+#pragma unroll
+    for (int h = 0; h < (SWIGLU ? 2 : 1); ++h)
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[h][i][j][0] = acc[h][i][j][1] = acc[h][i][j][2] = acc[h][i][j][3] = 0.f;
+    const int n_k = (K + BG_BK - 1) / BG_BK;
+    load_stage(0, 0);
+    for (int kt = 0; kt < n_k; ++kt) {
+        const int stage = kt & 1;
+        if (kt + 1 < n_k) { load_stage((kt + 1) * BG_BK, stage ^ 1); cp_async_wait<1>(); }
+        else cp_async_wait<0>();
+        __syncthreads();
+        const uint32_t ab = (uint32_t)__cvta_generic_to_shared(&a_s[stage][0]);
+        const uint32_t wb = (uint32_t)__cvta_generic_to_shared(&w_s[stage][0]);
+#pragma unroll
+        for (int ks = 0; ks < BG_BK / 16; ++ks) {
+            uint32_t af[2][4];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int r = wm + i * 16 + (lane & 15);
+                ldmatrix_x4(ab + (r * BG_LD + ks * 16 + (lane >> 4) * 8) * 2, af[i][0], af[i][1], af[i][2], af[i][3]);
+            }
+#pragma unroll
+            for (int h = 0; h < (SWIGLU ? 2 : 1); ++h)
+#pragma unroll
+                for (int jp = 0; jp < 2; ++jp) {               // two 8-column tiles per ldmatrix.x4
+                    uint32_t b0, b1, b2, b3;
+                    const int n = h * BG_BN + wn + jp * 16 + ((lane >> 4) << 3) + (lane & 7);
+                    ldmatrix_x4(wb + (n * BG_LD + ks * 16 + ((lane >> 3) & 1) * 8) * 2, b0, b1, b2, b3);
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        mma16816(acc[h][i][2 * jp], af[i][0], af[i][1], af[i][2], af[i][3], b0, b1);
+                        mma16816(acc[h][i][2 * jp + 1], af[i][0], af[i][1], af[i][2], af[i][3], b2, b3);
+                    }
+                }
+        }
+        __syncthreads();
+    }
+    // epilogue: thread holds rows (lane >> 2) and + 8 of each 16-row tile, columns 2 * (lane & 3) + {0, 1}
+    TC* C = (TC*)g.C + (size_t)e * g.c_batch;
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int hrow = 0; hrow < 2; ++hrow) {
+            const int r = r0 + wm + i * 16 + (lane >> 2) + hrow * 8;
+            if (r >= r_end) continue;
+            const size_t crow = g.c_index ? (size_t)g.c_index[r] : (size_t)r;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int x = 0; x < 2; ++x) {
+                    const int n = n0 + wn + j * 8 + 2 * (lane & 3) + x;
+                    if (n >= N) continue;
+                    float v = acc[0][i][j][hrow * 2 + x];
+                    if (SWIGLU) {
+                        const float u = acc[SWIGLU ? 1 : 0][i][j][hrow * 2 + x];
+                        v = v / (1.0f + __expf(-v)) * u;
+                    }
+                    C[crow * g.ldc + n] = ssb_from_float<TC>(v);
+                }
+        }
+}
+
+static int bg_launch(const BgArgs& a, int mode, int out_dtype, dim3 grid, int pdl, cudaStream_t stream) {
+    if (a.K <= 0 || a.K % 8 || a.lda % 8 || a.ldw % 8) return SSB_ERR_BAD_SIZE;
+    if ((((uintptr_t)a.A | (uintptr_t)a.W) & 15) || ((a.a_batch | a.w_batch) & 7)) return SSB_ERR_BAD_SIZE;
+    if (grid.y > 65535 || grid.z > 65535) return SSB_ERR_BAD_SIZE;
+    int rc;
+    if (mode == 1 && out_dtype == SSB_BF16)
+        rc = ssb_launch(batched_gemm_kernel<true, bf16>, grid, dim3(BG_THREADS), 0, stream, pdl != 0, a);
+    else if (mode == 0 && out_dtype == SSB_BF16)
+        rc = ssb_launch(batched_gemm_kernel<false, bf16>, grid, dim3(BG_THREADS), 0, stream, pdl != 0, a);
+    else if (mode == 0 && out_dtype == SSB_F32)
+        rc = ssb_launch(batched_gemm_kernel<false, float>, grid, dim3(BG_THREADS), 0, stream, pdl != 0, a);
+    else
+        return SSB_ERR_BAD_DTYPE;
+    return rc ? rc : ssb_launch_status();
+}
+
+// one matrix per head: C[t, h, :N] = W[h] (N x K) A[t, h, :K]; *_batch: elements between heads
+SSB_API int ssb_head_gemm_mma(const void* A, int lda, long long a_batch, const void* W, int ldw, long long w_batch,
+                              void* C, int ldc, long long c_batch, int out_dtype, int n_heads, int M, int N, int K,
+                              int pdl, cudaStream_t stream) {
+    if (M <= 0 || N <= 0 || n_heads <= 0) return 0;
+    BgArgs a = {};
+    a.A = (const bf16*)A; a.lda = lda; a.a_batch = a_batch; a.a_index = nullptr; a.a_div = 1;
+    a.W = (const bf16*)W; a.ldw = ldw; a.w_batch = w_batch;
+    a.C = C; a.ldc = ldc; a.c_batch = c_batch; a.c_index = nullptr;
+    a.M = M; a.N = N; a.K = K;
+    return bg_launch(a, 0, out_dtype, dim3((N + BG_BN - 1) / BG_BN, (M + BG_BM - 1) / BG_BM, n_heads), pdl, stream);
+}
+
+// one matrix per expert over the rows grouped for it (tiles of 64 rows).  mode 0: C = A W_e^T with N
+// columns; mode 1: W_e = [gate (N rows); up (N rows)], C = silu(A gate^T) * (A up^T)
+SSB_API int ssb_grouped_gemm_mma(const void* A, int lda, const int* a_index, int a_div, const void* W, int ldw,
+                                 long long w_expert, void* C, int ldc, const int* c_index, int out_dtype,
+                                 const int* offsets, const int* tile_expert, const int* tile_row0, const int* meta,
+                                 int max_tiles, int N, int K, int mode, int pdl, cudaStream_t stream) {
+    if (max_tiles <= 0 || N <= 0) return 0;
+    if (a_div <= 0) return SSB_ERR_BAD_SIZE;
+    BgArgs a = {};
+    a.A = (const bf16*)A; a.lda = lda; a.a_batch = 0; a.a_index = a_index; a.a_div = a_div;
+    a.W = (const bf16*)W; a.ldw = ldw; a.w_batch = w_expert;
+    a.C = C; a.ldc = ldc; a.c_batch = 0; a.c_index = c_index;
+    a.offsets = offsets; a.tile_expert = tile_expert; a.tile_row0 = tile_row0; a.meta = meta;
+    a.M = 0; a.N = N; a.K = K; a.up_row0 = N;
+    return bg_launch(a, mode, out_dtype, dim3((N + BG_BN - 1) / BG_BN, max_tiles, 1), pdl, stream);
+}

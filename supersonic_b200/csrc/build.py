@@ -42,6 +42,8 @@ LIBRARIES: Dict[str, Dict[str, List[str]]] = {
     "gemv_tc": {"sources": ["gemv_tc.cu"], "flags": [], "link": []},
     "gemm_tc": {"sources": ["gemm_tc.cu"], "flags": [], "link": []},
     "attention_decode_static": {"sources": ["attention_decode_static.cu"], "flags": [], "link": []},
+    "latent_attention": {"sources": ["latent_attention.cu"], "flags": [], "link": []},
+    "batched_gemm": {"sources": ["batched_gemm.cu"], "flags": [], "link": []},
     "latent_ops": {"sources": ["latent_ops.cu"], "flags": [], "link": []},
     "recurrence_ops": {"sources": ["recurrence_ops.cu"], "flags": [], "link": []},
     "expert_ops": {"sources": ["expert_ops.cu"], "flags": [], "link": []},

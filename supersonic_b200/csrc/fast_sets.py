@@ -314,3 +314,78 @@ class FastKernels(PlainKernels):
             return
         super().attention(q, k_cache, v_cache, batch, page_table, out, n_q, n_kv, head_dim, page_shift,
                           window, scale)
+
+    # ---- latent attention, per-head and per-expert products ---------------------------------------
+    LATENT_SPLIT_BLOCKS = 296      # a decode step cuts its sequences' pages until about two blocks an SM stream them
+
+    def head_linear(self, x, w, out):
+        if ops.head_gemm_mma_ok(x, w, out):
+            ops.head_gemm_mma(x, w, out, pdl=self.pdl)
+        else:
+            super().head_linear(x, w, out)
+
+    def latent_prepare(self, proj, c_off, q_abs, norm_w, eps, position, batch, page_table, cache, n_heads, dim,
+                       rot_dim, kv_rank, page_shift, write_cache=True):
+        cos, sin, rot_dims = position.rotary_tables()
+        ops.latent_prepare(proj, c_off, q_abs, norm_w, eps, cos, sin, batch.pos, batch.slot_of_token, page_table,
+                           cache, n_heads, dim, rot_dim, rot_dims, kv_rank, page_shift, write_cache,
+                           getattr(position, "interleaved", False), pdl=self.pdl)
+
+    def latent_attention(self, q_abs, cache, batch, page_table, out, n_heads, kv_rank, rot_dim, page_shift,
+                         window, scale, sinks):
+        dk = kv_rank + rot_dim
+        if not ops.latent_attention_mma_ok(q_abs, cache, out, n_heads, dk, kv_rank, page_shift):
+            super().latent_attention(q_abs, cache, batch, page_table, out, n_heads, kv_rank, rot_dim, page_shift,
+                                     window, scale, sinks)
+            return
+        splits, partial = 1, None
+        if batch.is_decode and not self.deterministic:
+            # the bucket's upper end: the most pages a sequence of this batch can span
+            pages = 2 * batch.kv_pages - 1 if batch.kv_pages > 1 else 1
+            if window:
+                pages = min(pages, (window >> page_shift) + 2)
+            blocks = batch.n_seqs * ((n_heads + 31) // 32)
+            splits = max(1, min(self.LATENT_SPLIT_BLOCKS // blocks, pages // 2, 64))
+            if splits > 1:
+                partial = self._buffer("latent_partials", batch.n_tokens * n_heads * splits * (kv_rank + 2),
+                                       torch.float32, q_abs.device)
+        ops.latent_attention_mma(q_abs, cache, batch.cu_new, batch.seq_start, batch.seq_slot, batch.slot_of_token,
+                                 page_table, out, sinks, batch.max_new, n_heads, dk, kv_rank, page_shift, window,
+                                 scale, splits, partial, pdl=self.pdl)
+
+    def gated_linear_scan(self, proj, q_off, k_off, v_off, z, z_bias, tau, q_scale, state, batch, out, n_heads,
+                          dim, vdim):
+        ops.gated_linear_scan(proj, q_off, k_off, v_off, z, z_bias, tau, q_scale, state, batch.cu_new,
+                              batch.seq_slot, out, n_heads, dim, vdim, pdl=self.pdl)
+
+    def head_norm_gate(self, o, weight, eps, gate, out, n_heads, vdim):
+        ops.head_norm_gate(o, weight, eps, gate, out, n_heads, vdim, pdl=self.pdl)
+
+    def route_table(self, token_ids, table, n_experts, expert_of, pair_weight):
+        ops.route_table(token_ids, table, n_experts, expert_of, pair_weight, pdl=self.pdl)
+
+    def group_by_expert(self, expert_of, n_experts, groups):
+        ops.group_by_expert(expert_of, n_experts, groups["tile_rows"], groups["offsets"], groups["order"],
+                            groups["tile_expert"], groups["tile_row0"], groups["meta"], pdl=self.pdl)
+
+    def grouped_linear(self, a, gather, top, w, out, scatter, groups):
+        if ops.grouped_gemm_mma_ok(a, w, out, ops.GG_STORE):
+            ops.grouped_gemm_mma(a, groups["order"] if gather else None, top if gather else 1, w, out,
+                                 groups["order"] if scatter else None, groups["offsets"], groups["tile_expert"],
+                                 groups["tile_row0"], groups["meta"], groups["max_tiles"], ops.GG_STORE, pdl=self.pdl)
+        else:
+            super().grouped_linear(a, gather, top, w, out, scatter, groups)
+
+    def expert_gate_up(self, x, top, w_gate_up, out, groups):
+        if ops.grouped_gemm_mma_ok(x, w_gate_up, out, ops.GG_SWIGLU):
+            ops.grouped_gemm_mma(x, groups["order"], top, w_gate_up, out, None, groups["offsets"],
+                                 groups["tile_expert"], groups["tile_row0"], groups["meta"], groups["max_tiles"],
+                                 ops.GG_SWIGLU, pdl=self.pdl)
+        else:
+            super().expert_gate_up(x, top, w_gate_up, out, groups)
+
+    def expert_combine(self, residual, y, pair_weight, top):
+        ops.expert_combine(residual, y, pair_weight, top, pdl=self.pdl)
+
+    def stream_mix(self, streams, weights, n_terms, out):
+        ops.stream_mix(streams, weights, n_terms, out, pdl=self.pdl)

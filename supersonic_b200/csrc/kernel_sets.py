@@ -150,6 +150,13 @@ class PlainKernels:
                                groups["order"] if scatter else None, groups["offsets"], groups["tile_expert"],
                                groups["tile_row0"], groups["meta"], groups["max_tiles"])
 
+    def expert_gate_up(self, x, top, w_gate_up, out, groups):
+        """out[sorted row] = silu(x gate_e^T) * (x up_e^T) for the row's expert e; ``w_gate_up`` [E, 2 * inter,
+        hidden] holds gate rows, then up rows; ``x``'s rows are tokens (gathered through the order)."""
+        gate_up = torch.empty((out.shape[0], w_gate_up.shape[1]), dtype=x.dtype, device=x.device)
+        self.grouped_linear(x, True, top, w_gate_up, gate_up, False, groups)
+        ops.swiglu(gate_up, out)
+
     def expert_combine(self, residual, y, pair_weight, top):
         ops.expert_combine(residual, y, pair_weight, top)
 

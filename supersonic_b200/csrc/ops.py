@@ -296,6 +296,95 @@ def latent_prepare(proj: torch.Tensor, c_off: int, q_abs: torch.Tensor, norm_w: 
         _stream()), "latent_prepare")
 
 
+def latent_attention_mma_ok(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, n_heads: int, dk: int, dv: int,
+                            page_shift: int) -> bool:
+    """Whether the tensor-core latent attention takes these operands (else the plain kernel does)."""
+    return (q.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+            and page_shift == 6 and dk % 16 == 0 and dv % 16 == 0 and 0 < dv <= min(dk, 512) and dk <= 656
+            and q.is_contiguous() and out.is_contiguous() and cache.is_contiguous()
+            and q.shape[1] == n_heads * dk and out.shape[1] == n_heads * dv
+            and q.data_ptr() % 16 == 0 and cache.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0)
+
+
+def latent_attention_mma(q: torch.Tensor, cache: torch.Tensor, cu_new: torch.Tensor, seq_start: torch.Tensor,
+                         seq_slot: torch.Tensor, slot_of_token: torch.Tensor, page_table: torch.Tensor,
+                         out: torch.Tensor, sinks: Optional[torch.Tensor], max_new: int, n_heads: int, dk: int,
+                         dv: int, page_shift: int, window: Optional[int], scale: float, n_splits: int = 1,
+                         partial: Optional[torch.Tensor] = None, pdl: bool = False) -> None:
+    """Every head of every new token over its sequence's cached rows [dv values | dk - dv more key elements]
+    (``cache`` [pages, 1, 64, dk]); ``q`` [tokens, heads x dk], ``out`` [tokens, heads x dv], both contiguous
+    bfloat16.  ``n_splits`` > 1 cuts a sequence's pages into that many parts whose results a second launch
+    merges through ``partial`` (float32, tokens x heads x n_splits x (dv + 2))."""
+    if not latent_attention_mma_ok(q, cache, out, n_heads, dk, dv, page_shift):
+        raise KernelError("latent_attention_mma: operands it does not take")
+    _need(cu_new, "cu_new", torch.int32, 1); _need(seq_start, "seq_start", torch.int32, 1)
+    _need(seq_slot, "seq_slot", torch.int32, 1); _need(slot_of_token, "slot_of_token", torch.int32, 1)
+    _need(page_table, "page_table", torch.int32, 2)
+    T, B = q.shape[0], seq_slot.shape[0]
+    if out.shape[0] != T or cu_new.shape[0] != B + 1 or seq_start.shape[0] != B or slot_of_token.shape[0] != T:
+        raise KernelError("latent_attention_mma: sizes")
+    if sinks is not None:
+        _need(sinks, "sinks", torch.float32, 1)
+        if sinks.shape[0] != n_heads:
+            raise KernelError("latent_attention_mma: one sink per head")
+    if n_splits > 1:
+        _need(partial, "partial", torch.float32)
+        if partial.numel() < T * n_heads * n_splits * (dv + 2):
+            raise KernelError("latent_attention_mma: the scratch for partial results is too small")
+    _check(_fn("latent_attention", "ssb_latent_attention")(
+        _ptr(q), _ptr(cache), _ptr(cu_new), _ptr(seq_start), _ptr(seq_slot), _ptr(slot_of_token), _ptr(page_table),
+        c_int(page_table.shape[1]), _ptr(out), _ptr(partial), _ptr(sinks), c_int(B), c_int(max_new), c_int(T),
+        c_int(n_heads), c_int(dk), c_int(dv), c_int(page_shift), c_int(int(window) if window else 0), c_float(scale),
+        c_int(n_splits), c_int(1 if pdl else 0), _stream()), "latent_attention_mma")
+
+
+# ---- many small matrix products on the tensor cores -------------------------------------------
+def head_gemm_mma_ok(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and out.dtype in (torch.bfloat16, torch.float32)
+            and x.dim() == 3 and w.dim() == 3 and w.is_contiguous() and x.stride(2) == 1 and out.stride(2) == 1
+            and x.shape[2] % 8 == 0 and x.stride(0) % 8 == 0 and x.stride(1) % 8 == 0
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def head_gemm_mma(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, pdl: bool = False) -> None:
+    """``head_linear_plain`` on mma.sync: out[t, h] = w[h] @ x[t, h] for bfloat16 operands."""
+    T, H, K = x.shape
+    N = w.shape[1]
+    if not head_gemm_mma_ok(x, w, out) or tuple(w.shape) != (H, N, K) or tuple(out.shape) != (T, H, N):
+        raise KernelError(f"head_gemm_mma: x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+    _check(_fn("batched_gemm", "ssb_head_gemm_mma")(
+        _ptr(x), c_int(x.stride(0)), c_longlong(x.stride(1)), _ptr(w), c_int(K), c_longlong(N * K), _ptr(out),
+        c_int(out.stride(0)), c_longlong(out.stride(1)), c_int(dtype_code(out.dtype)), c_int(H), c_int(T), c_int(N),
+        c_int(K), c_int(1 if pdl else 0), _stream()), "head_gemm_mma")
+
+
+GG_STORE, GG_SWIGLU = 0, 1
+
+
+def grouped_gemm_mma_ok(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int) -> bool:
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.is_contiguous() and a.shape[1] % 8 == 0
+            and a.stride(0) % 8 == 0 and a.stride(1) == 1 and out.stride(1) == 1 and a.data_ptr() % 16 == 0
+            and w.data_ptr() % 16 == 0 and (w.shape[1] * w.shape[2]) % 8 == 0
+            and (out.dtype == torch.bfloat16 or (mode == GG_STORE and out.dtype == torch.float32)))
+
+
+def grouped_gemm_mma(a: torch.Tensor, a_index: Optional[torch.Tensor], a_div: int, w: torch.Tensor,
+                     out: torch.Tensor, c_index: Optional[torch.Tensor], offsets: torch.Tensor,
+                     tile_expert: torch.Tensor, tile_row0: torch.Tensor, meta: torch.Tensor, max_tiles: int,
+                     mode: int = GG_STORE, pdl: bool = False) -> None:
+    """``grouped_gemm_plain`` on mma.sync (tiles of 64 rows).  mode GG_SWIGLU: ``w`` [E, 2N, K] holds gate rows then
+    up rows and ``out`` [rows, N] gets silu(a gate^T) * (a up^T)."""
+    E, n_w, K = w.shape
+    N = n_w // 2 if mode == GG_SWIGLU else n_w
+    if not grouped_gemm_mma_ok(a, w, out, mode) or a.shape[1] != K or out.shape[1] != N:
+        raise KernelError(f"grouped_gemm_mma: a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+    _check(_fn("batched_gemm", "ssb_grouped_gemm_mma")(
+        _ptr(a), c_int(a.stride(0)), _ptr(a_index), c_int(a_div), _ptr(w), c_int(K), c_longlong(n_w * K), _ptr(out),
+        c_int(out.stride(0)), _ptr(c_index), c_int(dtype_code(out.dtype)), _ptr(offsets), _ptr(tile_expert),
+        _ptr(tile_row0), _ptr(meta), c_int(max_tiles), c_int(N), c_int(K), c_int(mode), c_int(1 if pdl else 0),
+        _stream()), "grouped_gemm_mma")
+
+
 # ---- linear recurrences ----------------------------------------------------------------
 SCAN_MAX_DIM = 256
 

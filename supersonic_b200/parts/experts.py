@@ -109,10 +109,8 @@ class Experts:
                   "tile_expert": ints[self.E + 1 + P: self.E + 1 + P + max_tiles],
                   "tile_row0": ints[self.E + 1 + P + max_tiles: self.E + 1 + P + 2 * max_tiles], "meta": ints[-1:]}
         ctx.kernels.group_by_expert(expert_of, self.E, groups)
-        gate_up = torch.empty((P, 2 * self.inter), dtype=self.dtype, device=dev)
-        ctx.kernels.grouped_linear(xt, True, top, self.w_gate_up, gate_up, False, groups)
         z = torch.empty((P, self.inter), dtype=self.dtype, device=dev)
-        ctx.kernels.swiglu(gate_up, z)
+        ctx.kernels.expert_gate_up(xt, top, self.w_gate_up, z, groups)
         y = torch.empty((P, self.hidden), dtype=torch.float32, device=dev)
         ctx.kernels.grouped_linear(z, False, top, self.w_down, y, True, groups)
         ctx.kernels.expert_combine(residual, y, pair_weight, top)
