@@ -265,6 +265,153 @@ def time_e2e(engine, batch, prompt_len, steps, warmup, seed=2):
     return batch * steps / dt
 
 
+# ---- another design beside the closest existing model at equal size ----------------------------------
+def _sotavik_sizes(name):
+    """Configurations whose layers resemble a real model's: (Sotavik config.json, the Llama configuration of
+    the same width, layer count and vocabulary)."""
+    def latent(heads, dim, rot, vdim, rank):
+        return {"type": "latent_attention", "mixer": {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": vdim,
+                "kv_rank": rank, "rot": {"base": 10000.0, "dims": rot}, "scale": (dim + rot) ** -0.5}}
+
+    def gla(heads, dim, vdim):
+        return {"type": "gla", "mixer": {"heads": heads, "dim": dim, "vdim": vdim, "tau": 16.0, "decay_rank": 16}}
+
+    def moe(experts, top, ff, shared):
+        return {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top}, "shared": {"ff": shared}}
+    if name == "2048":
+        width, vocab = 2048, 32000
+        mixers = [latent(16, 128, 64, 128, 512), latent(16, 128, 64, 128, 512), gla(4, 256, 512), latent(16, 128, 64, 128, 512)]
+        mlp = moe(64, 6, 1408, 2816)
+        llama = dict(num_attention_heads=32, num_key_value_heads=8, head_dim=64, intermediate_size=8192)
+    elif name == "1024":
+        width, vocab = 1024, 32000
+        mixers = [latent(8, 64, 32, 64, 256), gla(4, 128, 256), latent(8, 64, 32, 64, 256), gla(4, 128, 256)]
+        mlp = moe(16, 2, 512, 1024)
+        llama = dict(num_attention_heads=16, num_key_value_heads=4, head_dim=64, intermediate_size=4096)
+    else:
+        raise SystemExit(f"--design-size {name!r}: known sizes are 1024 and 2048")
+    layers = [dict(m, mlp=mlp) for m in mixers]
+    sot = {"architecture": "Sotavik", "vocab": vocab, "width": width, "logit_scale": 1.0, "norm": {"eps": 1e-5},
+           "layers": layers}
+    lla = dict(architectures=["LlamaForCausalLM"], vocab_size=vocab, hidden_size=width, num_hidden_layers=len(layers),
+               max_position_embeddings=32768, rms_norm_eps=1e-5, rope_theta=10000.0, rope_scaling=None,
+               tie_word_embeddings=False, **llama)
+    return sot, lla
+
+
+def _operation_work(model, tokens):
+    """Algorithmic work of one prompt of ``tokens`` tokens per operation of the model's parts: (FLOPs, bytes).
+    Matrix products count 2 per multiply-add; attention counts its scores and weighted sums over the causal
+    half; the recurrence counts its float32 multiply-adds and the bytes it has to move."""
+    work = {}
+
+    def add(name, flops, nbytes=0):
+        f, b = work.get(name, (0, 0))
+        work[name] = (f + flops, b + nbytes)
+    T, causal = tokens, tokens * (tokens + 1) // 2
+    for b in model.blocks:
+        m, ff = b.mixer, b.feed_forward
+        kind = type(m).__name__
+        if kind == "LatentAttention":
+            add("mixer.linear", 2 * T * (m.w_in.numel() + m.w_o.numel()))
+            add("mixer.head_linear", 2 * T * (m.w_absorb.numel() + m.w_uv.numel()))
+            add("mixer.latent_attention", 2 * causal * m.H * (2 * m.rank + m.rot))
+        elif kind == "GatedLinearAttention":
+            add("mixer.linear", 2 * T * (m.w_in.numel() + m.w_a2.numel() + m.w_o.numel()))
+            add("mixer.gated_linear_scan", 4 * T * m.H * m.dim * m.vdim,
+                T * (2 * (2 * m.H * m.dim + m.H * m.vdim) + 4 * (m.H * m.dim + m.H * m.vdim)))
+        elif kind == "Attention":
+            add("mixer.linear", 2 * T * (m.w_qkv.numel() + m.w_o.numel()))
+            add("mixer.project_rope_append", 2 * T * m.w_qkv.numel())
+            add("mixer.attention", 4 * causal * m.n_q * m.head_dim)
+        fk = type(ff).__name__ if ff is not None else ""
+        if fk == "Experts":
+            per = ff.w_gate_up[0].numel() + ff.w_down[0].numel()
+            add("feed_forward.expert_gate_up", 2 * T * ff.top * ff.w_gate_up[0].numel())
+            add("feed_forward.grouped_linear", 2 * T * ff.top * ff.w_down[0].numel())
+            if ff.shared is not None:
+                add("feed_forward.gate_up_swiglu", 2 * T * ff.shared.w_gate_up.numel())
+                add("feed_forward.linear", 2 * T * ff.shared.w_down.numel())
+        elif fk == "SwiGLU":
+            add("feed_forward.gate_up_swiglu", 2 * T * ff.w_gate_up.numel())
+            add("feed_forward.linear", 2 * T * ff.w_down.numel())
+    return work
+
+
+def design_comparison(args):
+    """``--design sotavik``: prompts and decode steps of the Sotavik design at sizes that resemble a real
+    model's layers, beside a Llama model of the same width and depth, both with random bfloat16 weights;
+    and for a prompt, the device time of every operation of the parts against its own roofline."""
+    import torch
+    from supersonic_b200.config import config_from_dict
+    from supersonic_b200.engine import Model, StepEntry
+    from supersonic_b200.weights import RandomWeightStore
+    pk, pk_src = peaks()
+    sot, lla = _sotavik_sizes(args.design_size)
+    out = {"metric": "design_comparison", "design": "sotavik", "beside": "llama", "size": args.design_size,
+           "layers": len(sot["layers"]), "dtype": "bf16", "data": "synthetic", "peaks": pk, "peaks_source": pk_src,
+           "models": {}}
+    clocks = ClockSampler()
+    clocks.start()
+    for name, d in (("sotavik", sot), ("llama", lla)):
+        cfg = config_from_dict(d)
+        store = RandomWeightStore(cfg, seed=3, device="cuda:0", std=0.02, norm_jitter=0.0)
+        ctx = max(args.prefill_tokens, args.prompt_len) + 256
+        model = Model.from_config(cfg, store, dtype="bfloat16", device="cuda:0", max_tokens=72 * ctx, max_seq_tokens=ctx)
+        rec = {"weight_gib": round(model.weight_bytes() / 2**30, 3)}
+        for tokens in sorted({512, args.prefill_tokens}):
+            ms = time_prefill(model, tokens)
+            rec[f"prefill_{tokens}"] = {"ms": round(ms, 3), "tokens_per_s": round(tokens * 1000.0 / ms)}
+        for batch in (1, 8, 64):
+            ms, kernels, nbytes = time_decode(model, batch, args.prompt_len, max(args.steps // 2, 16), args.warmup)
+            for b in model.blocks:                            # a step reads the experts its tokens use, not all
+                ff = b.feed_forward
+                if type(ff).__name__ == "Experts":
+                    unused = (1.0 - ff.top / ff.E) ** batch
+                    nbytes -= int(unused * (ff.w_gate_up.numel() + ff.w_down.numel()) * ff.w_down.element_size())
+            rec[f"decode_{batch}x{args.prompt_len}"] = {
+                "ms": round(ms, 4), "tokens_per_s": round(batch * 1000.0 / ms), "kernels": kernels,
+                "gbs": round(nbytes / ms / 1e6, 1), "of_measured_hbm": round(nbytes / ms / 1e6 / pk["hbm_gbs"], 3)}
+        # every operation of a prompt, eagerly and bracketed by events, against its own work
+        tokens = args.prefill_tokens
+        work = _operation_work(model, tokens)
+        g = torch.Generator().manual_seed(9)
+        model.time_stages(True)
+        times = {}
+        for rep in range(4):
+            slot = model.open_sequence()
+            model.step([StepEntry(slot, torch.randint(0, model.vocab_size, (tokens,), generator=g).tolist(), [tokens - 1])])
+            got = model.stage_times(by_operation=True)
+            model.close_sequence(slot)
+            if rep:                                           # the first run builds and warms
+                for k, v in got.items():
+                    times[k] = min(times.get(k, v), v)
+        model.time_stages(False)
+        ops_rec = {}
+        for k, ms in sorted(times.items(), key=lambda kv: -kv[1]):
+            if ms < 0.002:
+                continue
+            r = {"ms": round(ms, 4)}
+            if k in work:
+                flops, nbytes = work[k]
+                if k == "mixer.linear" and times.get("mixer.project_rope_append", 0) >= 0.002:
+                    flops -= work["mixer.project_rope_append"][0]     # the fused projection took q/k/v
+                r["tflops"] = round(flops / ms / 1e9, 1)
+                roof_ms = flops / (pk["bf16_tflops"] * 1e9)
+                if nbytes:                                    # float32 arithmetic on the CUDA cores, or its bytes
+                    r["gbs"] = round(nbytes / ms / 1e6, 1)
+                    roof_ms = max(nbytes / (pk["hbm_gbs"] * 1e6), flops / (2 * 148 * 128 * 1.9e9 / 1e3))
+                r["of_roofline"] = round(roof_ms / ms, 4)
+            ops_rec[k] = r
+        rec[f"prefill_{tokens}_operations"] = ops_rec
+        out["models"][name] = rec
+        del model, store
+        torch.cuda.empty_cache()
+    out["clocks"] = clocks.stop()
+    print(json.dumps(out))
+    return 0
+
+
 def reference_arm(args):
     """The reference's whole engine cannot run here (Rust, no cargo in the image).  Its CUDA kernels
     can: compiled unmodified for sm_100a, the ones its Llama lane uses are timed per operation at the
@@ -374,8 +521,15 @@ def main():
                     help="also time decode and prompts at further sizes (adds a 'sweep' key to the line)")
     ap.add_argument("--deterministic", action="store_true",
                     help="time the bfloat16 path without float atomics and with one kernel choice whatever the batch")
+    ap.add_argument("--design", default=None, choices=["sotavik"],
+                    help="instead of the headline workload: this design beside the closest existing model at equal size")
+    ap.add_argument("--design-size", default="2048", help="width of the compared models: 1024 or 2048")
     args = ap.parse_args()
 
+    if args.design and args.impl != "reference":
+        if args.warmup < 3:
+            args.warmup = 3
+        return design_comparison(args)
     if args.impl == "reference":
         return reference_arm(args)
     if args.gpus != 1:

@@ -430,8 +430,8 @@ class Model:
         self._timed = TimedKernels(self.kernels) if on else None
         return self._timed
 
-    def stage_times(self):
-        return self._timed.collect() if self._timed is not None else {}
+    def stage_times(self, by_operation: bool = False):
+        return self._timed.collect(by_operation) if self._timed is not None else {}
 
     def _forward(self, batch: StepBatch) -> torch.Tensor:
         ctx = StepContext(batch, self.cache, self._timed or self.kernels, self.dtype)

@@ -22,7 +22,8 @@ from typing import Dict, List, Optional
 import torch
 
 STAGES = ("embed", "rms_norm", "full_attn_proj", "full_attn_core", "mlp", "lm_head", "sampling", "other")
-_CORE_OPS = {"attention", "rope_attention", "rope_append"}
+_CORE_OPS = {"attention", "rope_attention", "rope_append", "latent_attention", "latent_prepare", "gated_linear_scan",
+             "head_norm_gate"}
 
 
 def stage_of(part: str, op: str) -> str:
@@ -50,7 +51,7 @@ class TimedKernels:
         self._inner = inner
         self.ctx = None
         self._open: List[int] = []
-        self._records: List[list] = []       # [stage, start event, end event, parent index]
+        self._records: List[list] = []       # [stage, start event, end event, parent index, operation]
 
     def __getattr__(self, name):
         attr = getattr(self._inner, name)
@@ -61,7 +62,8 @@ class TimedKernels:
             part = getattr(self.ctx, "stage", "") if self.ctx is not None else ""
             start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             me = len(self._records)
-            self._records.append([stage_of(part, name), start, end, self._open[-1] if self._open else -1])
+            self._records.append([stage_of(part, name), start, end, self._open[-1] if self._open else -1,
+                                  f"{part}.{name}" if part else name])
             self._open.append(me)
             start.record()
             try:
@@ -71,17 +73,19 @@ class TimedKernels:
                 self._open.pop()
         return timed
 
-    def collect(self) -> Dict[str, float]:
-        """Milliseconds per stage since the last call (waits for the device)."""
+    def collect(self, by_operation: bool = False) -> Dict[str, float]:
+        """Milliseconds per stage since the last call (waits for the device); ``by_operation``: per
+        operation of each part ("mixer.latent_attention", "feed_forward.grouped_linear", ...) instead."""
         torch.cuda.synchronize()
         ms = [r[1].elapsed_time(r[2]) for r in self._records]
         own = list(ms)
         for i, r in enumerate(self._records):
             if r[3] >= 0:
                 own[r[3]] -= ms[i]
-        out = {s: 0.0 for s in STAGES}
+        out = {} if by_operation else {s: 0.0 for s in STAGES}
         for r, t in zip(self._records, own):
-            out[r[0]] += max(t, 0.0)
+            key = r[4] if by_operation else r[0]
+            out[key] = out.get(key, 0.0) + max(t, 0.0)
         self._records.clear()
         return out
 
