@@ -6,17 +6,18 @@
 // blockIdx.z and blockIdx.y (per-head form), or from the tile list that the grouping kernel wrote
 // (per-expert form: a block whose index is beyond the list's length returns).  Rows of A may be
 // gathered through an index (a_index[r] / a_div) and rows of C scattered through one, so that
-// tokens need not be copied into expert order.  The K range is walked 32 columns a stage through a
-// two-stage cp.async ring.  Epilogues: store (bfloat16 or float32), or SwiGLU: the matrix is
-// [gate rows; up rows] and the tile computes both halves for its columns and stores
-// silu(gate) * up.
+// tokens need not be copied into expert order.  The K range is walked 64 columns a stage through a
+// three-stage cp.async ring (two stages in flight while one is multiplied: a decode step's few rows
+// leave the weights' stream as the only work, and it must not wait for each stage in turn).
+// Epilogues: store (bfloat16 or float32), or SwiGLU: the matrix is [gate rows; up rows] and the
+// tile computes both halves for its columns and stores silu(gate) * up.
 #include "mma_helpers.cuh"
 #include <math.h>
 
 typedef __nv_bfloat16 bf16;
 
-constexpr int BG_BM = 64, BG_BN = 64, BG_BK = 32;
-constexpr int BG_LD = BG_BK + 8;                 // padded row of a stage in elements: 80 bytes, conflict-free ldmatrix
+constexpr int BG_BM = 64, BG_BN = 64, BG_BK = 64, BG_STAGES = 3;
+constexpr int BG_LD = BG_BK + 8;                 // padded row of a stage in elements: 144 bytes, conflict-free ldmatrix
 constexpr int BG_THREADS = 128;
 
 struct BgArgs {
@@ -31,8 +32,10 @@ struct BgArgs {
 template <bool SWIGLU, typename TC>
 __global__ void __launch_bounds__(BG_THREADS)
 batched_gemm_kernel(const BgArgs g) {
-    __shared__ __align__(16) bf16 a_s[2][BG_BM * BG_LD];
-    __shared__ __align__(16) bf16 w_s[2][(SWIGLU ? 2 : 1) * BG_BN * BG_LD];
+    extern __shared__ __align__(16) unsigned char bg_smem[];
+    constexpr int A_STAGE = BG_BM * BG_LD, W_STAGE = (SWIGLU ? 2 : 1) * BG_BN * BG_LD;
+    bf16* a_s = reinterpret_cast<bf16*>(bg_smem);                    // [stages][A_STAGE]
+    bf16* w_s = a_s + BG_STAGES * A_STAGE;                           // [stages][W_STAGE]
     __shared__ int a_rows[BG_BM];
     ssb_pdl_launch_dependents();
     ssb_pdl_wait();
@@ -58,17 +61,17 @@ batched_gemm_kernel(const BgArgs g) {
     __syncthreads();
     const int K = g.K, N = g.N;
     auto load_stage = [&](int k0, int stage) {
-        // 64 rows x 4 chunks of 8 elements for A, the same for W (twice for SwiGLU)
-        for (int c = tid; c < BG_BM * 4; c += BG_THREADS) {
-            const int r = c >> 2, ch = c & 3, k = k0 + ch * 8;
-            bf16* dst = &a_s[stage][r * BG_LD + ch * 8];
+        // 64 rows x 8 chunks of 8 elements for A, the same for W (twice for SwiGLU)
+        for (int c = tid; c < BG_BM * 8; c += BG_THREADS) {
+            const int r = c >> 3, ch = c & 7, k = k0 + ch * 8;
+            bf16* dst = a_s + stage * A_STAGE + r * BG_LD + ch * 8;
             const int m = a_rows[r];
             if (m >= 0 && k < K) cp_async16((uint32_t)__cvta_generic_to_shared(dst), A + (size_t)m * g.lda + k);
             else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
         }
-        for (int c = tid; c < (SWIGLU ? 2 : 1) * BG_BN * 4; c += BG_THREADS) {
-            const int r = c >> 2, ch = c & 3, k = k0 + ch * 8;
-            bf16* dst = &w_s[stage][r * BG_LD + ch * 8];
+        for (int c = tid; c < (SWIGLU ? 2 : 1) * BG_BN * 8; c += BG_THREADS) {
+            const int r = c >> 3, ch = c & 7, k = k0 + ch * 8;
+            bf16* dst = w_s + stage * W_STAGE + r * BG_LD + ch * 8;
             const int half = r / BG_BN, n = n0 + r % BG_BN;
             if (n < N && k < K) cp_async16((uint32_t)__cvta_generic_to_shared(dst),
                                            W + (size_t)(n + half * g.up_row0) * g.ldw + k);
@@ -86,14 +89,17 @@ batched_gemm_kernel(const BgArgs g) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) acc[h][i][j][0] = acc[h][i][j][1] = acc[h][i][j][2] = acc[h][i][j][3] = 0.f;
     const int n_k = (K + BG_BK - 1) / BG_BK;
+    // a group is committed every turn (an empty one past the end), so that "all but the newest one"
+    // always means: the stage about to be multiplied has landed
     load_stage(0, 0);
+    if (n_k > 1) load_stage(BG_BK, 1); else cp_async_commit();
     for (int kt = 0; kt < n_k; ++kt) {
-        const int stage = kt & 1;
-        if (kt + 1 < n_k) { load_stage((kt + 1) * BG_BK, stage ^ 1); cp_async_wait<1>(); }
-        else cp_async_wait<0>();
-        __syncthreads();
-        const uint32_t ab = (uint32_t)__cvta_generic_to_shared(&a_s[stage][0]);
-        const uint32_t wb = (uint32_t)__cvta_generic_to_shared(&w_s[stage][0]);
+        const int stage = kt % BG_STAGES;
+        cp_async_wait<1>();
+        __syncthreads();                                              // stage kt landed; stage kt - 1 is free
+        if (kt + 2 < n_k) load_stage((kt + 2) * BG_BK, (kt + 2) % BG_STAGES); else cp_async_commit();
+        const uint32_t ab = (uint32_t)__cvta_generic_to_shared(a_s + stage * A_STAGE);
+        const uint32_t wb = (uint32_t)__cvta_generic_to_shared(w_s + stage * W_STAGE);
 #pragma unroll
         for (int ks = 0; ks < BG_BK / 16; ++ks) {
             uint32_t af[2][4];
@@ -116,7 +122,6 @@ batched_gemm_kernel(const BgArgs g) {
                     }
                 }
         }
-        __syncthreads();
     }
     // epilogue: thread holds rows (lane >> 2) and + 8 of each 16-row tile, columns 2 * (lane & 3) + {0, 1}
     TC* C = (TC*)g.C + (size_t)e * g.c_batch;
@@ -148,14 +153,21 @@ static int bg_launch(const BgArgs& a, int mode, int out_dtype, dim3 grid, int pd
     if ((((uintptr_t)a.A | (uintptr_t)a.W) & 15) || ((a.a_batch | a.w_batch) & 7)) return SSB_ERR_BAD_SIZE;
     if (grid.y > 65535 || grid.z > 65535) return SSB_ERR_BAD_SIZE;
     int rc;
-    if (mode == 1 && out_dtype == SSB_BF16)
-        rc = ssb_launch(batched_gemm_kernel<true, bf16>, grid, dim3(BG_THREADS), 0, stream, pdl != 0, a);
-    else if (mode == 0 && out_dtype == SSB_BF16)
-        rc = ssb_launch(batched_gemm_kernel<false, bf16>, grid, dim3(BG_THREADS), 0, stream, pdl != 0, a);
-    else if (mode == 0 && out_dtype == SSB_F32)
-        rc = ssb_launch(batched_gemm_kernel<false, float>, grid, dim3(BG_THREADS), 0, stream, pdl != 0, a);
-    else
-        return SSB_ERR_BAD_DTYPE;
+#define SSB_BG(SW, TC) do { \
+        constexpr int smem = BG_STAGES * (BG_BM + (SW ? 2 : 1) * BG_BN) * BG_LD * 2; \
+        static bool configured = false; \
+        if (!configured) { \
+            cudaError_t e = cudaFuncSetAttribute(batched_gemm_kernel<SW, TC>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); \
+            if (e != cudaSuccess) return (int)e; \
+            configured = true; \
+        } \
+        rc = ssb_launch(batched_gemm_kernel<SW, TC>, grid, dim3(BG_THREADS), smem, stream, pdl != 0, a); \
+    } while (0)
+    if (mode == 1 && out_dtype == SSB_BF16) SSB_BG(true, bf16);
+    else if (mode == 0 && out_dtype == SSB_BF16) SSB_BG(false, bf16);
+    else if (mode == 0 && out_dtype == SSB_F32) SSB_BG(false, float);
+    else return SSB_ERR_BAD_DTYPE;
+#undef SSB_BG
     return rc ? rc : ssb_launch_status();
 }
 

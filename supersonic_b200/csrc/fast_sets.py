@@ -355,8 +355,14 @@ class FastKernels(PlainKernels):
 
     def gated_linear_scan(self, proj, q_off, k_off, v_off, z, z_bias, tau, q_scale, state, batch, out, n_heads,
                           dim, vdim):
+        chunk, n_sums, n_decays = ops.scan_chunking(batch.n_seqs, batch.max_new, n_heads, dim, vdim)
+        sums = decays = None
+        if chunk:
+            sums = self._buffer("scan_sums", n_sums, torch.float32, out.device)
+            decays = self._buffer("scan_decays", n_decays, torch.float32, out.device)
         ops.gated_linear_scan(proj, q_off, k_off, v_off, z, z_bias, tau, q_scale, state, batch.cu_new,
-                              batch.seq_slot, out, n_heads, dim, vdim, pdl=self.pdl)
+                              batch.seq_slot, out, n_heads, dim, vdim, pdl=self.pdl, chunk=chunk,
+                              max_new=batch.max_new, sums=sums, decays=decays)
 
     def head_norm_gate(self, o, weight, eps, gate, out, n_heads, vdim):
         ops.head_norm_gate(o, weight, eps, gate, out, n_heads, vdim, pdl=self.pdl)

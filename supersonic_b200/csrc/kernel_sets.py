@@ -125,8 +125,14 @@ class PlainKernels:
     # ---- linear recurrence -----------------------------------------------------------
     def gated_linear_scan(self, proj, q_off, k_off, v_off, z, z_bias, tau, q_scale, state, batch, out, n_heads,
                           dim, vdim):
+        chunk, n_sums, n_decays = ops.scan_chunking(batch.n_seqs, batch.max_new, n_heads, dim, vdim)
+        sums = decays = None
+        if chunk:                             # a long prompt: its chunks in parallel
+            sums = torch.empty(n_sums, dtype=torch.float32, device=out.device)
+            decays = torch.empty(n_decays, dtype=torch.float32, device=out.device)
         ops.gated_linear_scan(proj, q_off, k_off, v_off, z, z_bias, tau, q_scale, state, batch.cu_new,
-                              batch.seq_slot, out, n_heads, dim, vdim)
+                              batch.seq_slot, out, n_heads, dim, vdim, chunk=chunk, max_new=batch.max_new,
+                              sums=sums, decays=decays)
 
     def head_norm_gate(self, o, weight, eps, gate, out, n_heads, vdim):
         ops.head_norm_gate(o, weight, eps, gate, out, n_heads, vdim)

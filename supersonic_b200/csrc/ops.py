@@ -392,10 +392,15 @@ SCAN_MAX_DIM = 256
 def gated_linear_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, z: torch.Tensor,
                       z_bias: torch.Tensor, tau: float, q_scale: float, state: torch.Tensor,
                       cu_new: torch.Tensor, seq_slot: torch.Tensor, out: torch.Tensor, n_heads: int, dim: int,
-                      vdim: int, pdl: bool = False) -> None:
+                      vdim: int, pdl: bool = False, chunk: int = 0, max_new: int = 0,
+                      sums: Optional[torch.Tensor] = None, decays: Optional[torch.Tensor] = None) -> None:
     """Per sequence and head, over the sequence's new tokens in order:
     S = diag(sigmoid(z + z_bias)^(1/tau)) S + k v^T;  out = S^T (q * q_scale), with S [dim, vdim] float32 read
-    from and left in ``state[slot]``.  q, k (heads x dim) and v (heads x vdim) are columns of ``proj``."""
+    from and left in ``state[slot]``.  q, k (heads x dim) and v (heads x vdim) are columns of ``proj``.
+    ``chunk`` > 0: every sequence's tokens are cut into chunks of that many that run in parallel (each chunk's
+    own sum from zero, the state carried across the chunks in order, then the outputs of every chunk from the
+    state at its start), through the float32 scratch ``sums`` (sequences x chunks x heads x dim x vdim) and
+    ``decays`` (sequences x chunks x heads x dim), chunks = ceil(``max_new`` / chunk)."""
     _need(proj, "proj", None, 2); _need(z, "z", torch.float32, 2); _need(z_bias, "z_bias", torch.float32, 1)
     _need(state, "state", torch.float32, 2); _need(out, "out", torch.float32, 2)
     _need(cu_new, "cu_new", torch.int32, 1); _need(seq_slot, "seq_slot", torch.int32, 1)
@@ -407,11 +412,38 @@ def gated_linear_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, z:
         raise KernelError("gated_linear_scan: proj rows are too narrow")
     if state.shape[1] != n_heads * dim * vdim or not state.is_contiguous() or dim > SCAN_MAX_DIM:
         raise KernelError(f"gated_linear_scan: state rows of heads x dim x vdim, dim up to {SCAN_MAX_DIM}")
+    max_chunks = 0
+    if chunk > 0:
+        max_chunks = -(-max_new // chunk)
+        _need(sums, "sums", torch.float32); _need(decays, "decays", torch.float32)
+        if max_chunks < 1 or sums.numel() < B * max_chunks * n_heads * dim * vdim \
+                or decays.numel() < B * max_chunks * n_heads * dim:
+            raise KernelError("gated_linear_scan: the scratch of the chunked run is too small")
     _check(_fn("recurrence_ops", "ssb_gated_linear_scan")(
         _ptr(proj), c_int(proj.stride(0)), c_int(dtype_code(proj.dtype)), c_int(q_off), c_int(k_off), c_int(v_off),
         _ptr(z), c_int(z.stride(0)), _ptr(z_bias), c_float(tau), c_float(q_scale), _ptr(state), _ptr(cu_new),
         _ptr(seq_slot), _ptr(out), c_int(out.stride(0)), c_int(B), c_int(n_heads), c_int(dim), c_int(vdim),
-        c_int(1 if pdl else 0), _stream()), "gated_linear_scan")
+        c_int(chunk), c_int(max_chunks), _ptr(sums), _ptr(decays), c_int(1 if pdl else 0), _stream()),
+        "gated_linear_scan")
+
+
+SCAN_CHUNK = 64                  # tokens of a chunk when a long prompt's recurrence runs chunk-parallel
+SCAN_CHUNK_MIN_NEW = 192         # shorter runs of new tokens are walked in one go
+SCAN_SCRATCH_BYTES = 1 << 30     # the most the chunk sums of a step may take
+
+
+def scan_chunking(n_seqs: int, max_new: int, n_heads: int, dim: int, vdim: int):
+    """(chunk, floats of sums, floats of decays) for a step's recurrence; chunk 0: walk every sequence in one
+    go.  The chunk grows beyond SCAN_CHUNK where the sums of all chunks would not fit the scratch bound."""
+    if max_new < SCAN_CHUNK_MIN_NEW:
+        return 0, 0, 0
+    per = n_heads * dim * vdim
+    most = SCAN_SCRATCH_BYTES // (4 * per * n_seqs)
+    if most < 2:
+        return 0, 0, 0
+    chunk = max(SCAN_CHUNK, -(-max_new // most))
+    n = -(-max_new // chunk)
+    return chunk, n_seqs * n * per, n_seqs * n * n_heads * dim
 
 
 def head_norm_gate(o: torch.Tensor, weight: torch.Tensor, eps: float, gate: torch.Tensor, out: torch.Tensor,

@@ -22,44 +22,76 @@ __device__ __forceinline__ float log_sigmoid(float z) {
     return fminf(z, 0.f) - log1pf(expf(-fabsf(z)));
 }
 
+// One kernel serves three uses.  A block walks tokens [t_lo, t_hi) of one sequence for one head and one
+// tile of value columns:
+//   whole run   (chunk = 0): from the slot's state, writing outputs, leaving the state in the slot;
+//   chunk sums  (chunk > 0, sums != null, out == null): from zero over chunk blockIdx.x % max_chunks of the
+//               sequence, leaving the chunk's own sum in ``sums`` and the product of its decays in ``decays``;
+//   chunk outputs (chunk > 0, out != null): from the state at the chunk's start, which the carry kernel below
+//               left in ``sums``, writing outputs.
+// A long prompt is run as chunk sums, carry, chunk outputs: the chunks of a sequence in parallel, the same
+// float32 recurrence within each.  The next token's inputs are fetched while the current one is worked on.
 template <typename T>
 __global__ void __launch_bounds__(SCAN_COLS * SCAN_GROUPS)
 gated_linear_scan_kernel(const T* __restrict__ proj, int ld, int q_off, int k_off, int v_off,
                          const float* __restrict__ z, int ldz, const float* __restrict__ z_bias,
                          float inv_tau, float q_scale, float* __restrict__ state,
                          const int* __restrict__ cu_new, const int* __restrict__ seq_slot,
-                         float* __restrict__ out, int ldo, int n_heads, int dim, int vdim) {
+                         float* __restrict__ out, int ldo, int n_heads, int dim, int vdim,
+                         int chunk, int max_chunks, float* __restrict__ sums, float* __restrict__ decays) {
     extern __shared__ float sm[];
     float* a_s = sm;                    // [dim] decay
     float* k_s = a_s + dim;             // [dim]
     float* q_s = k_s + dim;             // [dim]
     float* v_s = q_s + dim;             // [SCAN_COLS]
     float* o_s = v_s + SCAN_COLS;       // [SCAN_GROUPS][SCAN_COLS]
-    const int b = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * SCAN_COLS;
+    const int b = chunk > 0 ? blockIdx.x / max_chunks : blockIdx.x, c = chunk > 0 ? blockIdx.x % max_chunks : 0;
+    const int h = blockIdx.y, j0 = blockIdx.z * SCAN_COLS;
     const int tid = threadIdx.x, j = tid % SCAN_COLS, g = tid / SCAN_COLS;
     ssb_pdl_launch_dependents();
     ssb_pdl_wait();
     const int slot = seq_slot[b];
     if (slot < 0) return;                                // padding row
-    const int t0 = cu_new[b], t1 = cu_new[b + 1];
+    int t0 = cu_new[b], t1 = cu_new[b + 1];
+    if (chunk > 0) {
+        t0 += c * chunk;
+        t1 = min(t1, t0 + chunk);
+        if (t0 >= t1) return;
+    }
     const bool col = j0 + j < vdim;
-    float* S = state + ((size_t)slot * n_heads + h) * dim * vdim;
+    const bool emit = out != nullptr;
+    float* S = chunk > 0 ? sums + (((size_t)blockIdx.x * n_heads + h) * dim) * vdim
+                         : state + ((size_t)slot * n_heads + h) * dim * vdim;
     float s_reg[SCAN_MAX_ROWS];
 #pragma unroll
     for (int r = 0; r < SCAN_MAX_ROWS; ++r) {
         const int i = g + r * SCAN_GROUPS;
-        s_reg[r] = (col && i < dim) ? S[(size_t)i * vdim + j0 + j] : 0.f;
+        s_reg[r] = (col && i < dim && (chunk == 0 || emit)) ? S[(size_t)i * vdim + j0 + j] : 0.f;
     }
-    for (int t = t0; t < t1; ++t) {
+    // this thread's share of a token's inputs: channel tid of z, k, q (dim <= the block's threads) and value
+    // column tid of the tile
+    float zz = 0.f, kk = 0.f, qq = 0.f, vv = 0.f, a_prod = 1.f;
+    auto fetch = [&](int t) {
         const T* row = proj + (size_t)t * ld;
-        for (int i = tid; i < dim; i += SCAN_COLS * SCAN_GROUPS) {
-            const float zz = z[(size_t)t * ldz + h * dim + i] + z_bias[h * dim + i];
-            a_s[i] = expf(log_sigmoid(zz) * inv_tau);
-            k_s[i] = ssb_to_float(row[k_off + h * dim + i]);
-            q_s[i] = ssb_to_float(row[q_off + h * dim + i]) * q_scale;
+        if (tid < dim) {
+            zz = z[(size_t)t * ldz + h * dim + tid] + z_bias[h * dim + tid];
+            kk = ssb_to_float(row[k_off + h * dim + tid]);
+            qq = ssb_to_float(row[q_off + h * dim + tid]);
         }
-        if (tid < SCAN_COLS) v_s[tid] = (j0 + tid < vdim) ? ssb_to_float(row[v_off + h * vdim + j0 + tid]) : 0.f;
+        if (tid < SCAN_COLS) vv = (j0 + tid < vdim) ? ssb_to_float(row[v_off + h * vdim + j0 + tid]) : 0.f;
+    };
+    fetch(t0);
+    for (int t = t0; t < t1; ++t) {
+        if (tid < dim) {
+            const float a = expf(log_sigmoid(zz) * inv_tau);
+            a_prod *= a;
+            a_s[tid] = a;
+            k_s[tid] = kk;
+            q_s[tid] = qq * q_scale;
+        }
+        if (tid < SCAN_COLS) v_s[tid] = vv;
         __syncthreads();
+        if (t + 1 < t1) fetch(t + 1);
         const float v = v_s[j];
         float o = 0.f;
 #pragma unroll
@@ -70,46 +102,104 @@ gated_linear_scan_kernel(const T* __restrict__ proj, int ld, int q_off, int k_of
                 o = fmaf(s_reg[r], q_s[i], o);
             }
         }
-        o_s[g * SCAN_COLS + j] = o;
+        if (emit) o_s[g * SCAN_COLS + j] = o;
         __syncthreads();
-        if (g == 0 && col) {
+        if (emit && g == 0 && col) {
             float sum = 0.f;
 #pragma unroll
             for (int gg = 0; gg < SCAN_GROUPS; ++gg) sum += o_s[gg * SCAN_COLS + j];
             out[(size_t)t * ldo + h * vdim + j0 + j] = sum;
         }
     }
+    if (chunk > 0 && emit) return;                       // the state was carried by the carry kernel
 #pragma unroll
     for (int r = 0; r < SCAN_MAX_ROWS; ++r) {
         const int i = g + r * SCAN_GROUPS;
         if (col && i < dim) S[(size_t)i * vdim + j0 + j] = s_reg[r];
     }
+    if (chunk > 0 && blockIdx.z == 0 && tid < dim) decays[((size_t)blockIdx.x * n_heads + h) * dim + tid] = a_prod;
+}
+
+// Carries the state across a sequence's chunks: with S the state before chunk c, chunk c's place in
+// ``sums`` gets S (what the chunk starts from) and S <- decays[c] * S + sums[c]; the last S is the
+// sequence's state.  One thread per state element, chunks in order.
+__global__ void __launch_bounds__(256)
+gated_linear_carry_kernel(float* __restrict__ state, float* __restrict__ sums, const float* __restrict__ decays,
+                          const int* __restrict__ cu_new, const int* __restrict__ seq_slot, int n_heads, int dim,
+                          int vdim, int chunk, int max_chunks) {
+    ssb_pdl_launch_dependents();
+    ssb_pdl_wait();
+    const int b = blockIdx.y, slot = seq_slot[b];
+    if (slot < 0) return;
+    const size_t per = (size_t)n_heads * dim * vdim;
+    const size_t e = (size_t)blockIdx.x * 256 + threadIdx.x;
+    if (e >= per) return;
+    const size_t hi = e / vdim;                          // head * dim + channel
+    const int n_chunks = (cu_new[b + 1] - cu_new[b] + chunk - 1) / chunk;
+    float cur = state[(size_t)slot * per + e];
+    float* sp = sums + (size_t)b * max_chunks * per + e;
+    const float* dp = decays + (size_t)b * max_chunks * n_heads * dim + hi;
+    float loc = n_chunks > 0 ? sp[0] : 0.f, a = n_chunks > 0 ? dp[0] : 0.f;
+    for (int c = 0; c < n_chunks; ++c) {
+        float loc_n = 0.f, a_n = 0.f;
+        if (c + 1 < n_chunks) {
+            loc_n = sp[(size_t)(c + 1) * per];
+            a_n = dp[(size_t)(c + 1) * n_heads * dim];
+        }
+        sp[(size_t)c * per] = cur;
+        cur = fmaf(a, cur, loc);
+        loc = loc_n;
+        a = a_n;
+    }
+    state[(size_t)slot * per + e] = cur;
 }
 
 // proj [T, ld] holds q, k (n_heads x dim each) and v (n_heads x vdim) from the given columns;
 // z [T, ldz] float32 is the decay's pre-activation without its bias z_bias [n_heads x dim];
-// state [slots, n_heads, dim, vdim] float32; out [T, ldo] float32 gets o (n_heads x vdim)
+// state [slots, n_heads, dim, vdim] float32; out [T, ldo] float32 gets o (n_heads x vdim).
+// chunk > 0: sequences are run in chunks of that many tokens, in parallel, through ``sums``
+// (n_seqs x max_chunks x n_heads x dim x vdim floats) and ``decays`` (n_seqs x max_chunks x n_heads x dim);
+// max_chunks = ceil(longest run of new tokens / chunk).
 SSB_API int ssb_gated_linear_scan(const void* proj, int ld, int dtype, int q_off, int k_off, int v_off,
                                   const float* z, int ldz, const float* z_bias, float tau, float q_scale,
                                   float* state, const int* cu_new, const int* seq_slot, float* out, int ldo,
-                                  int n_seqs, int n_heads, int dim, int vdim, int pdl, cudaStream_t stream) {
+                                  int n_seqs, int n_heads, int dim, int vdim, int chunk, int max_chunks,
+                                  float* sums, float* decays, int pdl, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
     if (dim <= 0 || dim > SCAN_MAX_ROWS * SCAN_GROUPS || vdim <= 0 || !(tau > 0.f)) return SSB_ERR_BAD_SIZE;
-    const dim3 grid(n_seqs, n_heads, (vdim + SCAN_COLS - 1) / SCAN_COLS);
-    if (grid.y > 65535 || grid.z > 65535) return SSB_ERR_BAD_SIZE;
+    if (chunk < 0 || (chunk > 0 && (max_chunks <= 0 || sums == nullptr || decays == nullptr))) return SSB_ERR_BAD_SIZE;
+    const long long items = chunk > 0 ? (long long)n_seqs * max_chunks : n_seqs;
+    if (items > 0x7fffffffll) return SSB_ERR_BAD_SIZE;
+    const dim3 grid((unsigned)items, n_heads, (vdim + SCAN_COLS - 1) / SCAN_COLS);
+    if (grid.y > 65535 || grid.z > 65535 || n_seqs > 65535) return SSB_ERR_BAD_SIZE;
     const size_t smem = (3 * (size_t)dim + SCAN_COLS + SCAN_COLS * SCAN_GROUPS) * sizeof(float);
-    int rc;
-    if (dtype == SSB_F32)
-        rc = ssb_launch(gated_linear_scan_kernel<float>, grid, dim3(SCAN_COLS * SCAN_GROUPS), smem, stream, pdl != 0,
-                        (const float*)proj, ld, q_off, k_off, v_off, z, ldz, z_bias, 1.0f / tau, q_scale, state, cu_new,
-                        seq_slot, out, ldo, n_heads, dim, vdim);
-    else if (dtype == SSB_BF16)
-        rc = ssb_launch(gated_linear_scan_kernel<bf16>, grid, dim3(SCAN_COLS * SCAN_GROUPS), smem, stream, pdl != 0,
-                        (const bf16*)proj, ld, q_off, k_off, v_off, z, ldz, z_bias, 1.0f / tau, q_scale, state, cu_new,
-                        seq_slot, out, ldo, n_heads, dim, vdim);
-    else
-        return SSB_ERR_BAD_DTYPE;
-    return rc ? rc : ssb_launch_status();
+    const float inv_tau = 1.0f / tau;
+    int rc = 0;
+#define SSB_SCAN(T, OUT) \
+    rc = ssb_launch(gated_linear_scan_kernel<T>, grid, dim3(SCAN_COLS * SCAN_GROUPS), smem, stream, pdl != 0, \
+                    (const T*)proj, ld, q_off, k_off, v_off, z, ldz, z_bias, inv_tau, q_scale, state, cu_new, seq_slot, \
+                    OUT, ldo, n_heads, dim, vdim, chunk, max_chunks, sums, decays)
+#define SSB_SCAN_BOTH(OUT) do { \
+        if (dtype == SSB_F32) SSB_SCAN(float, OUT); \
+        else if (dtype == SSB_BF16) SSB_SCAN(bf16, OUT); \
+        else return SSB_ERR_BAD_DTYPE; \
+        if (!rc) rc = ssb_launch_status(); \
+        if (rc) return rc; \
+    } while (0)
+    if (chunk == 0) {
+        SSB_SCAN_BOTH(out);
+        return 0;
+    }
+    SSB_SCAN_BOTH((float*)nullptr);
+    const size_t per = (size_t)n_heads * dim * vdim;
+    rc = ssb_launch(gated_linear_carry_kernel, dim3((unsigned)((per + 255) / 256), n_seqs), dim3(256), 0, stream, pdl != 0,
+                    state, sums, (const float*)decays, cu_new, seq_slot, n_heads, dim, vdim, chunk, max_chunks);
+    if (!rc) rc = ssb_launch_status();
+    if (rc) return rc;
+    SSB_SCAN_BOTH(out);
+#undef SSB_SCAN_BOTH
+#undef SSB_SCAN
+    return 0;
 }
 
 // ---------------------------------------------------------------------------------------
