@@ -6,8 +6,8 @@
 // blockIdx.z and blockIdx.y (per-head form), or from the tile list that the grouping kernel wrote
 // (per-expert form: a block whose index is beyond the list's length returns).  Rows of A may be
 // gathered through an index (a_index[r] / a_div) and rows of C scattered through one, so that
-// tokens need not be copied into expert order.  The K range is walked 64 columns a stage through a
-// three-stage cp.async ring (two stages in flight while one is multiplied: a decode step's few rows
+// tokens need not be copied into expert order.  The K range is walked 32 columns a stage through a
+// four-stage cp.async ring (three stages in flight while one is multiplied: a decode step's few rows
 // leave the weights' stream as the only work, and it must not wait for each stage in turn).
 // Epilogues: store (bfloat16 or float32), or SwiGLU: the matrix is [gate rows; up rows] and the
 // tile computes both halves for its columns and stores silu(gate) * up.
@@ -16,8 +16,8 @@
 
 typedef __nv_bfloat16 bf16;
 
-constexpr int BG_BM = 64, BG_BN = 64, BG_BK = 64, BG_STAGES = 3;
-constexpr int BG_LD = BG_BK + 8;                 // padded row of a stage in elements: 144 bytes, conflict-free ldmatrix
+constexpr int BG_BM = 64, BG_BN = 64, BG_BK = 32, BG_STAGES = 4;
+constexpr int BG_LD = BG_BK + 8;                 // padded row of a stage in elements: 80 bytes, conflict-free ldmatrix
 constexpr int BG_THREADS = 128;
 
 struct BgArgs {
@@ -61,16 +61,16 @@ batched_gemm_kernel(const BgArgs g) {
     __syncthreads();
     const int K = g.K, N = g.N;
     auto load_stage = [&](int k0, int stage) {
-        // 64 rows x 8 chunks of 8 elements for A, the same for W (twice for SwiGLU)
-        for (int c = tid; c < BG_BM * 8; c += BG_THREADS) {
-            const int r = c >> 3, ch = c & 7, k = k0 + ch * 8;
+        // 64 rows x 4 chunks of 8 elements for A, the same for W (twice for SwiGLU)
+        for (int c = tid; c < BG_BM * 4; c += BG_THREADS) {
+            const int r = c >> 2, ch = c & 3, k = k0 + ch * 8;
             bf16* dst = a_s + stage * A_STAGE + r * BG_LD + ch * 8;
             const int m = a_rows[r];
             if (m >= 0 && k < K) cp_async16((uint32_t)__cvta_generic_to_shared(dst), A + (size_t)m * g.lda + k);
             else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
         }
-        for (int c = tid; c < (SWIGLU ? 2 : 1) * BG_BN * 8; c += BG_THREADS) {
-            const int r = c >> 3, ch = c & 7, k = k0 + ch * 8;
+        for (int c = tid; c < (SWIGLU ? 2 : 1) * BG_BN * 4; c += BG_THREADS) {
+            const int r = c >> 2, ch = c & 3, k = k0 + ch * 8;
             bf16* dst = w_s + stage * W_STAGE + r * BG_LD + ch * 8;
             const int half = r / BG_BN, n = n0 + r % BG_BN;
             if (n < N && k < K) cp_async16((uint32_t)__cvta_generic_to_shared(dst),
@@ -91,13 +91,16 @@ batched_gemm_kernel(const BgArgs g) {
     const int n_k = (K + BG_BK - 1) / BG_BK;
     // a group is committed every turn (an empty one past the end), so that "all but the newest one"
     // always means: the stage about to be multiplied has landed
-    load_stage(0, 0);
-    if (n_k > 1) load_stage(BG_BK, 1); else cp_async_commit();
+#pragma unroll
+    for (int p = 0; p < BG_STAGES - 1; ++p) {
+        if (p < n_k) load_stage(p * BG_BK, p); else cp_async_commit();
+    }
     for (int kt = 0; kt < n_k; ++kt) {
         const int stage = kt % BG_STAGES;
-        cp_async_wait<1>();
+        cp_async_wait<BG_STAGES - 2>();
         __syncthreads();                                              // stage kt landed; stage kt - 1 is free
-        if (kt + 2 < n_k) load_stage((kt + 2) * BG_BK, (kt + 2) % BG_STAGES); else cp_async_commit();
+        const int ahead = kt + BG_STAGES - 1;
+        if (ahead < n_k) load_stage(ahead * BG_BK, ahead % BG_STAGES); else cp_async_commit();
         const uint32_t ab = (uint32_t)__cvta_generic_to_shared(a_s + stage * A_STAGE);
         const uint32_t wb = (uint32_t)__cvta_generic_to_shared(w_s + stage * W_STAGE);
 #pragma unroll

@@ -16,6 +16,8 @@ typedef __nv_bfloat16 bf16;
 constexpr int SCAN_COLS = 32;        // value columns a block owns
 constexpr int SCAN_GROUPS = 8;       // row groups: thread (g, j) owns rows g, g + 8, ... of column j
 constexpr int SCAN_MAX_ROWS = 32;    // rows per thread: dim up to 256
+constexpr int SCAN_TOKENS = 4;       // tokens staged in shared memory a turn (one pair of barriers for all of them)
+constexpr int SCAN_ITEMS = SCAN_TOKENS * SCAN_MAX_ROWS * SCAN_GROUPS / (SCAN_COLS * SCAN_GROUPS);   // staged items a thread
 
 __device__ __forceinline__ float log_sigmoid(float z) {
     // log(1 / (1 + exp(-z))) without overflow on either side
@@ -30,7 +32,8 @@ __device__ __forceinline__ float log_sigmoid(float z) {
 //   chunk outputs (chunk > 0, out != null): from the state at the chunk's start, which the carry kernel below
 //               left in ``sums``, writing outputs.
 // A long prompt is run as chunk sums, carry, chunk outputs: the chunks of a sequence in parallel, the same
-// float32 recurrence within each.  The next token's inputs are fetched while the current one is worked on.
+// float32 recurrence within each.  Tokens are staged four at a time, and the next four are fetched while
+// these are worked on.
 template <typename T>
 __global__ void __launch_bounds__(SCAN_COLS * SCAN_GROUPS)
 gated_linear_scan_kernel(const T* __restrict__ proj, int ld, int q_off, int k_off, int v_off,
@@ -39,12 +42,16 @@ gated_linear_scan_kernel(const T* __restrict__ proj, int ld, int q_off, int k_of
                          const int* __restrict__ cu_new, const int* __restrict__ seq_slot,
                          float* __restrict__ out, int ldo, int n_heads, int dim, int vdim,
                          int chunk, int max_chunks, float* __restrict__ sums, float* __restrict__ decays) {
-    extern __shared__ float sm[];
-    float* a_s = sm;                    // [dim] decay
-    float* k_s = a_s + dim;             // [dim]
-    float* q_s = k_s + dim;             // [dim]
-    float* v_s = q_s + dim;             // [SCAN_COLS]
-    float* o_s = v_s + SCAN_COLS;       // [SCAN_GROUPS][SCAN_COLS]
+    constexpr int NT = SCAN_COLS * SCAN_GROUPS;
+    extern __shared__ __align__(16) float sm[];
+    // rows per thread, a multiple of four: thread (g, j) owns rows g * rpt .. + rpt - 1 of column j, and reads
+    // their decays, keys and queries four at a time; the arrays are padded with zeros up to 8 * rpt rows
+    const int rpt = ((dim + SCAN_GROUPS - 1) / SCAN_GROUPS + 3) & ~3, dimp = rpt * SCAN_GROUPS;
+    float* a_s = sm;                          // [SCAN_TOKENS][dimp] decays
+    float* k_s = a_s + SCAN_TOKENS * dimp;    // [SCAN_TOKENS][dimp]
+    float* q_s = k_s + SCAN_TOKENS * dimp;    // [SCAN_TOKENS][dimp]
+    float* v_s = q_s + SCAN_TOKENS * dimp;    // [SCAN_TOKENS][SCAN_COLS]
+    float* o_s = v_s + SCAN_TOKENS * SCAN_COLS;   // [SCAN_TOKENS][SCAN_GROUPS][SCAN_COLS]
     const int b = chunk > 0 ? blockIdx.x / max_chunks : blockIdx.x, c = chunk > 0 ? blockIdx.x % max_chunks : 0;
     const int h = blockIdx.y, j0 = blockIdx.z * SCAN_COLS;
     const int tid = threadIdx.x, j = tid % SCAN_COLS, g = tid / SCAN_COLS;
@@ -65,57 +72,80 @@ gated_linear_scan_kernel(const T* __restrict__ proj, int ld, int q_off, int k_of
     float s_reg[SCAN_MAX_ROWS];
 #pragma unroll
     for (int r = 0; r < SCAN_MAX_ROWS; ++r) {
-        const int i = g + r * SCAN_GROUPS;
-        s_reg[r] = (col && i < dim && (chunk == 0 || emit)) ? S[(size_t)i * vdim + j0 + j] : 0.f;
+        const int i = g * rpt + r;
+        s_reg[r] = (col && r < rpt && i < dim && (chunk == 0 || emit)) ? S[(size_t)i * vdim + j0 + j] : 0.f;
     }
-    // this thread's share of a token's inputs: channel tid of z, k, q (dim <= the block's threads) and value
-    // column tid of the tile
-    float zz = 0.f, kk = 0.f, qq = 0.f, vv = 0.f, a_prod = 1.f;
+    for (int e = tid; e < 3 * SCAN_TOKENS * dimp; e += NT) sm[e] = 0.f;      // the padding stays zero
+    // a turn stages SCAN_TOKENS tokens: item (token, channel) n * NT + tid of the turn is this thread's
+    float zz[SCAN_ITEMS], kk[SCAN_ITEMS], qq[SCAN_ITEMS], vv = 0.f, a_prod = 1.f;
     auto fetch = [&](int t) {
-        const T* row = proj + (size_t)t * ld;
-        if (tid < dim) {
-            zz = z[(size_t)t * ldz + h * dim + tid] + z_bias[h * dim + tid];
-            kk = ssb_to_float(row[k_off + h * dim + tid]);
-            qq = ssb_to_float(row[q_off + h * dim + tid]);
-        }
-        if (tid < SCAN_COLS) vv = (j0 + tid < vdim) ? ssb_to_float(row[v_off + h * vdim + j0 + tid]) : 0.f;
-    };
-    fetch(t0);
-    for (int t = t0; t < t1; ++t) {
-        if (tid < dim) {
-            const float a = expf(log_sigmoid(zz) * inv_tau);
-            a_prod *= a;
-            a_s[tid] = a;
-            k_s[tid] = kk;
-            q_s[tid] = qq * q_scale;
-        }
-        if (tid < SCAN_COLS) v_s[tid] = vv;
-        __syncthreads();
-        if (t + 1 < t1) fetch(t + 1);
-        const float v = v_s[j];
-        float o = 0.f;
+        const int n_tok = min(SCAN_TOKENS, t1 - t);
 #pragma unroll
-        for (int r = 0; r < SCAN_MAX_ROWS; ++r) {
-            const int i = g + r * SCAN_GROUPS;
-            if (i < dim) {
-                s_reg[r] = fmaf(a_s[i], s_reg[r], k_s[i] * v);
-                o = fmaf(s_reg[r], q_s[i], o);
+        for (int n = 0; n < SCAN_ITEMS; ++n) {
+            const int item = n * NT + tid, tt = item / dim, i = item % dim;
+            if (item < SCAN_TOKENS * dim && tt < n_tok) {
+                const T* row = proj + (size_t)(t + tt) * ld;
+                zz[n] = z[(size_t)(t + tt) * ldz + h * dim + i] + z_bias[h * dim + i];
+                kk[n] = ssb_to_float(row[k_off + h * dim + i]);
+                qq[n] = ssb_to_float(row[q_off + h * dim + i]);
             }
         }
-        if (emit) o_s[g * SCAN_COLS + j] = o;
-        __syncthreads();
-        if (emit && g == 0 && col) {
-            float sum = 0.f;
+        if (tid < SCAN_TOKENS * SCAN_COLS) {
+            const int tt = tid / SCAN_COLS, jj = tid % SCAN_COLS;
+            vv = (tt < n_tok && j0 + jj < vdim) ? ssb_to_float(proj[(size_t)(t + tt) * ld + v_off + h * vdim + j0 + jj]) : 0.f;
+        }
+    };
+    fetch(t0);
+    __syncthreads();
+    for (int t = t0; t < t1; t += SCAN_TOKENS) {
+        const int n_tok = min(SCAN_TOKENS, t1 - t);
 #pragma unroll
-            for (int gg = 0; gg < SCAN_GROUPS; ++gg) sum += o_s[gg * SCAN_COLS + j];
-            out[(size_t)t * ldo + h * vdim + j0 + j] = sum;
+        for (int n = 0; n < SCAN_ITEMS; ++n) {
+            const int item = n * NT + tid, tt = item / dim, i = item % dim;
+            if (item < SCAN_TOKENS * dim && tt < n_tok) {
+                a_s[tt * dimp + i] = expf(log_sigmoid(zz[n]) * inv_tau);
+                k_s[tt * dimp + i] = kk[n];
+                q_s[tt * dimp + i] = qq[n] * q_scale;
+            }
+        }
+        if (tid < SCAN_TOKENS * SCAN_COLS) v_s[tid] = vv;
+        __syncthreads();
+        if (t + SCAN_TOKENS < t1) fetch(t + SCAN_TOKENS);
+        if (decays != nullptr && tid < dim)
+            for (int tt = 0; tt < n_tok; ++tt) a_prod *= a_s[tt * dimp + tid];
+        for (int tt = 0; tt < n_tok; ++tt) {
+            const float v = v_s[tt * SCAN_COLS + j];
+            const float4* a4 = reinterpret_cast<const float4*>(a_s + tt * dimp + g * rpt);
+            const float4* k4 = reinterpret_cast<const float4*>(k_s + tt * dimp + g * rpt);
+            const float4* q4 = reinterpret_cast<const float4*>(q_s + tt * dimp + g * rpt);
+            float o = 0.f;
+#pragma unroll
+            for (int r = 0; r < SCAN_MAX_ROWS; r += 4)
+                if (r < rpt) {
+                    const float4 a = a4[r >> 2], k = k4[r >> 2], q = q4[r >> 2];
+                    s_reg[r] = fmaf(a.x, s_reg[r], k.x * v);          o = fmaf(s_reg[r], q.x, o);
+                    s_reg[r + 1] = fmaf(a.y, s_reg[r + 1], k.y * v);  o = fmaf(s_reg[r + 1], q.y, o);
+                    s_reg[r + 2] = fmaf(a.z, s_reg[r + 2], k.z * v);  o = fmaf(s_reg[r + 2], q.z, o);
+                    s_reg[r + 3] = fmaf(a.w, s_reg[r + 3], k.w * v);  o = fmaf(s_reg[r + 3], q.w, o);
+                }
+            if (emit) o_s[(tt * SCAN_GROUPS + g) * SCAN_COLS + j] = o;
+        }
+        __syncthreads();
+        if (emit && tid < n_tok * SCAN_COLS) {
+            const int tt = tid / SCAN_COLS, jj = tid % SCAN_COLS;
+            if (j0 + jj < vdim) {
+                float sum = 0.f;
+#pragma unroll
+                for (int gg = 0; gg < SCAN_GROUPS; ++gg) sum += o_s[(tt * SCAN_GROUPS + gg) * SCAN_COLS + jj];
+                out[(size_t)(t + tt) * ldo + h * vdim + j0 + jj] = sum;
+            }
         }
     }
     if (chunk > 0 && emit) return;                       // the state was carried by the carry kernel
 #pragma unroll
     for (int r = 0; r < SCAN_MAX_ROWS; ++r) {
-        const int i = g + r * SCAN_GROUPS;
-        if (col && i < dim) S[(size_t)i * vdim + j0 + j] = s_reg[r];
+        const int i = g * rpt + r;
+        if (col && r < rpt && i < dim) S[(size_t)i * vdim + j0 + j] = s_reg[r];
     }
     if (chunk > 0 && blockIdx.z == 0 && tid < dim) decays[((size_t)blockIdx.x * n_heads + h) * dim + tid] = a_prod;
 }
@@ -172,7 +202,8 @@ SSB_API int ssb_gated_linear_scan(const void* proj, int ld, int dtype, int q_off
     if (items > 0x7fffffffll) return SSB_ERR_BAD_SIZE;
     const dim3 grid((unsigned)items, n_heads, (vdim + SCAN_COLS - 1) / SCAN_COLS);
     if (grid.y > 65535 || grid.z > 65535 || n_seqs > 65535) return SSB_ERR_BAD_SIZE;
-    const size_t smem = (3 * (size_t)dim + SCAN_COLS + SCAN_COLS * SCAN_GROUPS) * sizeof(float);
+    const int rpt = ((dim + SCAN_GROUPS - 1) / SCAN_GROUPS + 3) & ~3;
+    const size_t smem = (size_t)SCAN_TOKENS * (3 * rpt * SCAN_GROUPS + SCAN_COLS + SCAN_COLS * SCAN_GROUPS) * sizeof(float);
     const float inv_tau = 1.0f / tau;
     int rc = 0;
 #define SSB_SCAN(T, OUT) \
