@@ -396,7 +396,8 @@ def gated_linear_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, z:
                       sums: Optional[torch.Tensor] = None, decays: Optional[torch.Tensor] = None) -> None:
     """Per sequence and head, over the sequence's new tokens in order:
     S = diag(sigmoid(z + z_bias)^(1/tau)) S + k v^T;  out = S^T (q * q_scale), with S [dim, vdim] float32 read
-    from and left in ``state[slot]``.  q, k (heads x dim) and v (heads x vdim) are columns of ``proj``.
+    from and left in ``state[slot]``.  q, k (heads x dim) and v (heads x vdim) are columns of ``proj``; ``z`` is
+    overwritten with the decays.
     ``chunk`` > 0: every sequence's tokens are cut into chunks of that many that run in parallel (each chunk's
     own sum from zero, the state carried across the chunks in order, then the outputs of every chunk from the
     state at its start), through the float32 scratch ``sums`` (sequences x chunks x heads x dim x vdim) and
@@ -422,7 +423,7 @@ def gated_linear_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, z:
     _check(_fn("recurrence_ops", "ssb_gated_linear_scan")(
         _ptr(proj), c_int(proj.stride(0)), c_int(dtype_code(proj.dtype)), c_int(q_off), c_int(k_off), c_int(v_off),
         _ptr(z), c_int(z.stride(0)), _ptr(z_bias), c_float(tau), c_float(q_scale), _ptr(state), _ptr(cu_new),
-        _ptr(seq_slot), _ptr(out), c_int(out.stride(0)), c_int(B), c_int(n_heads), c_int(dim), c_int(vdim),
+        _ptr(seq_slot), _ptr(out), c_int(out.stride(0)), c_int(B), c_int(T), c_int(n_heads), c_int(dim), c_int(vdim),
         c_int(chunk), c_int(max_chunks), _ptr(sums), _ptr(decays), c_int(1 if pdl else 0), _stream()),
         "gated_linear_scan")
 

@@ -14,8 +14,8 @@
 typedef __nv_bfloat16 bf16;
 
 constexpr int SCAN_COLS = 32;        // value columns a block owns
-constexpr int SCAN_GROUPS = 8;       // row groups: thread (g, j) owns rows g, g + 8, ... of column j
-constexpr int SCAN_MAX_ROWS = 32;    // rows per thread: dim up to 256
+constexpr int SCAN_GROUPS = 16;      // row groups: thread (g, j) owns a run of rows of column j
+constexpr int SCAN_MAX_ROWS = 16;    // rows per thread: dim up to 256
 constexpr int SCAN_TOKENS = 4;       // tokens staged in shared memory a turn (one pair of barriers for all of them)
 constexpr int SCAN_ITEMS = SCAN_TOKENS * SCAN_MAX_ROWS * SCAN_GROUPS / (SCAN_COLS * SCAN_GROUPS);   // staged items a thread
 
@@ -34,11 +34,24 @@ __device__ __forceinline__ float log_sigmoid(float z) {
 // A long prompt is run as chunk sums, carry, chunk outputs: the chunks of a sequence in parallel, the same
 // float32 recurrence within each.  Tokens are staged four at a time, and the next four are fetched while
 // these are worked on.
+// z <- sigmoid(z + bias)^(1 / tau), in place: the decays of every token and channel, once for all the blocks
+// that walk them
+__global__ void decay_kernel(float* __restrict__ z, int ldz, const float* __restrict__ z_bias, float inv_tau,
+                             int width, size_t total) {
+    ssb_pdl_launch_dependents();
+    ssb_pdl_wait();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const size_t t = idx / width;
+    const int c = (int)(idx % width);
+    float* p = z + t * ldz + c;
+    *p = expf(log_sigmoid(*p + z_bias[c]) * inv_tau);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(SCAN_COLS * SCAN_GROUPS)
 gated_linear_scan_kernel(const T* __restrict__ proj, int ld, int q_off, int k_off, int v_off,
-                         const float* __restrict__ z, int ldz, const float* __restrict__ z_bias,
-                         float inv_tau, float q_scale, float* __restrict__ state,
+                         const float* __restrict__ z, int ldz, float q_scale, float* __restrict__ state,
                          const int* __restrict__ cu_new, const int* __restrict__ seq_slot,
                          float* __restrict__ out, int ldo, int n_heads, int dim, int vdim,
                          int chunk, int max_chunks, float* __restrict__ sums, float* __restrict__ decays) {
@@ -85,7 +98,7 @@ gated_linear_scan_kernel(const T* __restrict__ proj, int ld, int q_off, int k_of
             const int item = n * NT + tid, tt = item / dim, i = item % dim;
             if (item < SCAN_TOKENS * dim && tt < n_tok) {
                 const T* row = proj + (size_t)(t + tt) * ld;
-                zz[n] = z[(size_t)(t + tt) * ldz + h * dim + i] + z_bias[h * dim + i];
+                zz[n] = z[(size_t)(t + tt) * ldz + h * dim + i];
                 kk[n] = ssb_to_float(row[k_off + h * dim + i]);
                 qq[n] = ssb_to_float(row[q_off + h * dim + i]);
             }
@@ -103,7 +116,7 @@ gated_linear_scan_kernel(const T* __restrict__ proj, int ld, int q_off, int k_of
         for (int n = 0; n < SCAN_ITEMS; ++n) {
             const int item = n * NT + tid, tt = item / dim, i = item % dim;
             if (item < SCAN_TOKENS * dim && tt < n_tok) {
-                a_s[tt * dimp + i] = expf(log_sigmoid(zz[n]) * inv_tau);
+                a_s[tt * dimp + i] = zz[n];
                 k_s[tt * dimp + i] = kk[n];
                 q_s[tt * dimp + i] = qq[n] * q_scale;
             }
@@ -185,17 +198,18 @@ gated_linear_carry_kernel(float* __restrict__ state, float* __restrict__ sums, c
 }
 
 // proj [T, ld] holds q, k (n_heads x dim each) and v (n_heads x vdim) from the given columns;
-// z [T, ldz] float32 is the decay's pre-activation without its bias z_bias [n_heads x dim];
+// z [T, ldz] float32 is the decay's pre-activation without its bias z_bias [n_heads x dim], and is overwritten
+// with the decays;
 // state [slots, n_heads, dim, vdim] float32; out [T, ldo] float32 gets o (n_heads x vdim).
 // chunk > 0: sequences are run in chunks of that many tokens, in parallel, through ``sums``
 // (n_seqs x max_chunks x n_heads x dim x vdim floats) and ``decays`` (n_seqs x max_chunks x n_heads x dim);
 // max_chunks = ceil(longest run of new tokens / chunk).
 SSB_API int ssb_gated_linear_scan(const void* proj, int ld, int dtype, int q_off, int k_off, int v_off,
-                                  const float* z, int ldz, const float* z_bias, float tau, float q_scale,
+                                  float* z, int ldz, const float* z_bias, float tau, float q_scale,
                                   float* state, const int* cu_new, const int* seq_slot, float* out, int ldo,
-                                  int n_seqs, int n_heads, int dim, int vdim, int chunk, int max_chunks,
+                                  int n_seqs, int n_tokens, int n_heads, int dim, int vdim, int chunk, int max_chunks,
                                   float* sums, float* decays, int pdl, cudaStream_t stream) {
-    if (n_seqs <= 0) return 0;
+    if (n_seqs <= 0 || n_tokens <= 0) return 0;
     if (dim <= 0 || dim > SCAN_MAX_ROWS * SCAN_GROUPS || vdim <= 0 || !(tau > 0.f)) return SSB_ERR_BAD_SIZE;
     if (chunk < 0 || (chunk > 0 && (max_chunks <= 0 || sums == nullptr || decays == nullptr))) return SSB_ERR_BAD_SIZE;
     const long long items = chunk > 0 ? (long long)n_seqs * max_chunks : n_seqs;
@@ -204,11 +218,17 @@ SSB_API int ssb_gated_linear_scan(const void* proj, int ld, int dtype, int q_off
     if (grid.y > 65535 || grid.z > 65535 || n_seqs > 65535) return SSB_ERR_BAD_SIZE;
     const int rpt = ((dim + SCAN_GROUPS - 1) / SCAN_GROUPS + 3) & ~3;
     const size_t smem = (size_t)SCAN_TOKENS * (3 * rpt * SCAN_GROUPS + SCAN_COLS + SCAN_COLS * SCAN_GROUPS) * sizeof(float);
-    const float inv_tau = 1.0f / tau;
     int rc = 0;
+    {
+        const size_t total = (size_t)n_tokens * n_heads * dim;
+        rc = ssb_launch(decay_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, pdl != 0, z, ldz, z_bias,
+                        1.0f / tau, n_heads * dim, total);
+        if (!rc) rc = ssb_launch_status();
+        if (rc) return rc;
+    }
 #define SSB_SCAN(T, OUT) \
     rc = ssb_launch(gated_linear_scan_kernel<T>, grid, dim3(SCAN_COLS * SCAN_GROUPS), smem, stream, pdl != 0, \
-                    (const T*)proj, ld, q_off, k_off, v_off, z, ldz, z_bias, inv_tau, q_scale, state, cu_new, seq_slot, \
+                    (const T*)proj, ld, q_off, k_off, v_off, (const float*)z, ldz, q_scale, state, cu_new, seq_slot, \
                     OUT, ldo, n_heads, dim, vdim, chunk, max_chunks, sums, decays)
 #define SSB_SCAN_BOTH(OUT) do { \
         if (dtype == SSB_F32) SSB_SCAN(float, OUT); \
