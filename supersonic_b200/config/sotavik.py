@@ -130,6 +130,10 @@ class SotavikConfig:
 
     # ---- what other parts of the framework ask ---------------------------------------
     @property
+    def architectures(self) -> List[str]:
+        return [ARCHITECTURE]
+
+    @property
     def vocab_size(self) -> int:
         return self.vocab
 

@@ -77,3 +77,13 @@ def test_preflight_counts_every_part():
     from supersonic_b200.cache import KvNeed, StateNeed
     needs = preflight.cache_needs(cfg.build_spec())
     assert needs[0] == StateNeed(1 * 40 * 72) and needs[1] == KvNeed(1, 44, None, value_dim=0)
+
+
+def test_preset_and_command_line_names():
+    from supersonic_b200.config import preset_config, preset_names
+    assert "sotavik-small" in preset_names()
+    cfg = preset_config("sotavik-small")
+    assert cfg.architectures == ["Sotavik"] and cfg.model_type == "sotavik"
+    spec = cfg.build_spec()
+    assert {b.mixer.kind for b in spec.blocks} == {"latent_attention", "gated_linear_attention"}
+    assert cfg.parameter_count() > 100_000_000
