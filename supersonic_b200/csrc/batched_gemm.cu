@@ -7,8 +7,10 @@
 // (per-expert form: a block whose index is beyond the list's length returns).  Rows of A may be
 // gathered through an index (a_index[r] / a_div) and rows of C scattered through one, so that
 // tokens need not be copied into expert order.  The K range is walked 32 columns a stage through a
-// four-stage cp.async ring (three stages in flight while one is multiplied: a decode step's few rows
-// leave the weights' stream as the only work, and it must not wait for each stage in turn).
+// cp.async ring of two or four stages.  Four (three in flight while one is multiplied) when few rows
+// leave the weights' stream as the only work, which must not wait for each stage in turn: a decode
+// step.  Two when the tiles are full: then what counts is how many blocks an SM holds (seven of
+// 30 KB against three of 61 KB: 2,048 tokens' gate/up of 64 experts 2.6 ms against 3.1 ms).
 // Epilogues: store (bfloat16 or float32), or SwiGLU: the matrix is [gate rows; up rows] and the
 // tile computes both halves for its columns and stores silu(gate) * up.
 #include "mma_helpers.cuh"
@@ -16,7 +18,7 @@
 
 typedef __nv_bfloat16 bf16;
 
-constexpr int BG_BM = 64, BG_BN = 64, BG_BK = 32, BG_STAGES = 4;
+constexpr int BG_BM = 64, BG_BN = 64, BG_BK = 32;
 constexpr int BG_LD = BG_BK + 8;                 // padded row of a stage in elements: 80 bytes, conflict-free ldmatrix
 constexpr int BG_THREADS = 128;
 
@@ -29,7 +31,7 @@ struct BgArgs {
     int up_row0;                                  // SwiGLU: first row of the up half in a matrix
 };
 
-template <bool SWIGLU, typename TC>
+template <bool SWIGLU, typename TC, int BG_STAGES>
 __global__ void __launch_bounds__(BG_THREADS)
 batched_gemm_kernel(const BgArgs g) {
     extern __shared__ __align__(16) unsigned char bg_smem[];
@@ -151,26 +153,28 @@ batched_gemm_kernel(const BgArgs g) {
         }
 }
 
-static int bg_launch(const BgArgs& a, int mode, int out_dtype, dim3 grid, int pdl, cudaStream_t stream) {
+static int bg_launch(const BgArgs& a, int mode, int out_dtype, dim3 grid, int deep, int pdl, cudaStream_t stream) {
     if (a.K <= 0 || a.K % 8 || a.lda % 8 || a.ldw % 8) return SSB_ERR_BAD_SIZE;
     if ((((uintptr_t)a.A | (uintptr_t)a.W) & 15) || ((a.a_batch | a.w_batch) & 7)) return SSB_ERR_BAD_SIZE;
     if (grid.y > 65535 || grid.z > 65535) return SSB_ERR_BAD_SIZE;
     int rc;
-#define SSB_BG(SW, TC) do { \
-        constexpr int smem = BG_STAGES * (BG_BM + (SW ? 2 : 1) * BG_BN) * BG_LD * 2; \
+#define SSB_BG_ST(SW, TC, ST) do { \
+        constexpr int smem = ST * (BG_BM + (SW ? 2 : 1) * BG_BN) * BG_LD * 2; \
         static bool configured = false; \
         if (!configured) { \
-            cudaError_t e = cudaFuncSetAttribute(batched_gemm_kernel<SW, TC>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); \
+            cudaError_t e = cudaFuncSetAttribute(batched_gemm_kernel<SW, TC, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); \
             if (e != cudaSuccess) return (int)e; \
             configured = true; \
         } \
-        rc = ssb_launch(batched_gemm_kernel<SW, TC>, grid, dim3(BG_THREADS), smem, stream, pdl != 0, a); \
+        rc = ssb_launch(batched_gemm_kernel<SW, TC, ST>, grid, dim3(BG_THREADS), smem, stream, pdl != 0, a); \
     } while (0)
+#define SSB_BG(SW, TC) do { if (deep) SSB_BG_ST(SW, TC, 4); else SSB_BG_ST(SW, TC, 2); } while (0)
     if (mode == 1 && out_dtype == SSB_BF16) SSB_BG(true, bf16);
     else if (mode == 0 && out_dtype == SSB_BF16) SSB_BG(false, bf16);
     else if (mode == 0 && out_dtype == SSB_F32) SSB_BG(false, float);
     else return SSB_ERR_BAD_DTYPE;
 #undef SSB_BG
+#undef SSB_BG_ST
     return rc ? rc : ssb_launch_status();
 }
 
@@ -178,13 +182,14 @@ static int bg_launch(const BgArgs& a, int mode, int out_dtype, dim3 grid, int pd
 SSB_API int ssb_head_gemm_mma(const void* A, int lda, long long a_batch, const void* W, int ldw, long long w_batch,
                               void* C, int ldc, long long c_batch, int out_dtype, int n_heads, int M, int N, int K,
                               int pdl, cudaStream_t stream) {
+    // M rows of every head: a deep ring when the rows are few
     if (M <= 0 || N <= 0 || n_heads <= 0) return 0;
     BgArgs a = {};
     a.A = (const bf16*)A; a.lda = lda; a.a_batch = a_batch; a.a_index = nullptr; a.a_div = 1;
     a.W = (const bf16*)W; a.ldw = ldw; a.w_batch = w_batch;
     a.C = C; a.ldc = ldc; a.c_batch = c_batch; a.c_index = nullptr;
     a.M = M; a.N = N; a.K = K;
-    return bg_launch(a, 0, out_dtype, dim3((N + BG_BN - 1) / BG_BN, (M + BG_BM - 1) / BG_BM, n_heads), pdl, stream);
+    return bg_launch(a, 0, out_dtype, dim3((N + BG_BN - 1) / BG_BN, (M + BG_BM - 1) / BG_BM, n_heads), M <= 256, pdl, stream);
 }
 
 // one matrix per expert over the rows grouped for it (tiles of 64 rows).  mode 0: C = A W_e^T with N
@@ -192,7 +197,8 @@ SSB_API int ssb_head_gemm_mma(const void* A, int lda, long long a_batch, const v
 SSB_API int ssb_grouped_gemm_mma(const void* A, int lda, const int* a_index, int a_div, const void* W, int ldw,
                                  long long w_expert, void* C, int ldc, const int* c_index, int out_dtype,
                                  const int* offsets, const int* tile_expert, const int* tile_row0, const int* meta,
-                                 int max_tiles, int N, int K, int mode, int pdl, cudaStream_t stream) {
+                                 int max_tiles, int n_rows, int N, int K, int mode, int pdl, cudaStream_t stream) {
+    // n_rows: the rows of all groups together (what the host knows of their sizes)
     if (max_tiles <= 0 || N <= 0) return 0;
     if (a_div <= 0) return SSB_ERR_BAD_SIZE;
     BgArgs a = {};
@@ -201,5 +207,5 @@ SSB_API int ssb_grouped_gemm_mma(const void* A, int lda, const int* a_index, int
     a.C = C; a.ldc = ldc; a.c_batch = 0; a.c_index = c_index;
     a.offsets = offsets; a.tile_expert = tile_expert; a.tile_row0 = tile_row0; a.meta = meta;
     a.M = 0; a.N = N; a.K = K; a.up_row0 = N;
-    return bg_launch(a, mode, out_dtype, dim3((N + BG_BN - 1) / BG_BN, max_tiles, 1), pdl, stream);
+    return bg_launch(a, mode, out_dtype, dim3((N + BG_BN - 1) / BG_BN, max_tiles, 1), n_rows <= 1024, pdl, stream);
 }

@@ -114,6 +114,7 @@ latent_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cac
         {
             const uint32_t qa = qb + ((rg * 16 + (lane & 15)) * ldk + (lane >> 4) * 8) * 2;
             const uint32_t ka = kbase + ((kw * 16 + ((lane >> 4) << 3) + (lane & 7)) * ldk + ((lane >> 3) & 1) * 8) * 2;
+#pragma unroll 4
             for (int ks = 0; ks < (dk >> 4); ++ks) {
                 uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
                 ldmatrix_x4(qa + ks * 32, a0, a1, a2, a3);

@@ -361,6 +361,11 @@ def head_gemm_mma(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, pdl: bool
 GG_STORE, GG_SWIGLU = 0, 1
 
 
+def order_rows(a, a_index, out, c_index) -> int:
+    """Rows of all groups together, from whichever operand is in sorted order."""
+    return int(out.shape[0] if c_index is None else a.shape[0] if a_index is None else a_index.shape[0])
+
+
 def grouped_gemm_mma_ok(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int) -> bool:
     return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.is_contiguous() and a.shape[1] % 8 == 0
             and a.stride(0) % 8 == 0 and a.stride(1) == 1 and out.stride(1) == 1 and a.data_ptr() % 16 == 0
@@ -381,8 +386,8 @@ def grouped_gemm_mma(a: torch.Tensor, a_index: Optional[torch.Tensor], a_div: in
     _check(_fn("batched_gemm", "ssb_grouped_gemm_mma")(
         _ptr(a), c_int(a.stride(0)), _ptr(a_index), c_int(a_div), _ptr(w), c_int(K), c_longlong(n_w * K), _ptr(out),
         c_int(out.stride(0)), _ptr(c_index), c_int(dtype_code(out.dtype)), _ptr(offsets), _ptr(tile_expert),
-        _ptr(tile_row0), _ptr(meta), c_int(max_tiles), c_int(N), c_int(K), c_int(mode), c_int(1 if pdl else 0),
-        _stream()), "grouped_gemm_mma")
+        _ptr(tile_row0), _ptr(meta), c_int(max_tiles), c_int(order_rows(a, a_index, out, c_index)), c_int(N), c_int(K),
+        c_int(mode), c_int(1 if pdl else 0), _stream()), "grouped_gemm_mma")
 
 
 # ---- linear recurrences ----------------------------------------------------------------
