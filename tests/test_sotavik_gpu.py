@@ -190,7 +190,7 @@ def test_unequal_batches_against_each_alone_and_reused_slots(dtype):
     from supersonic_b200.engine import StepEntry
     cfg, store, plain = ts.build("Q")
     model = make_model(cfg, store, dtype, max_tokens=1024)
-    # the third round's long prompts run their recurrences chunk-parallel beside short ones that do not fill a chunk
+    # the third group's long prompts run their recurrences chunk-parallel beside short ones that do not fill a chunk
     for round_, lens in enumerate(([1, 5, 64, 65, 131], [131, 2, 66], [260, 3, 195, 64], [7, 129, 64, 3])):
         decode = [3, 9, 14, 6, 11][: len(lens)]
         seqs = [tokens_of(cfg, n + d, 100 * round_ + i) for i, (n, d) in enumerate(zip(lens, decode))]
