@@ -6,6 +6,10 @@ so that weights come from DRAM), and reports bytes or FLOPs per second.
     python microbench.py attention_prefill --tokens 2048 --seqs 1 [--kernel tc]
     python microbench.py gemm --rows 2048 --n 28672 --k 4096 --tile 256
     python microbench.py sampling --rows 64 --vocab 128256 --temperature 0.7 --top-k 40 --top-p 0.9
+    python microbench.py latent_attention --tokens 2048 --heads 16 --k 576 --n 512
+    python microbench.py latent_attention --tokens 1 --batch 64 --context 520 --splits 2 --heads 16 --k 576 --n 512
+    python microbench.py grouped_gemm --tokens 2048 --experts 64 --top 6 --n 1408 --k 2048 --kernel swiglu
+    python microbench.py gated_linear_scan --tokens 2048 --heads 4 --k 256 --n 512 --chunk 128
 
 One JSON line per run.  It is also the small, self-ending workload that profiler captures
 are taken on.
@@ -157,6 +161,72 @@ def attention_prefill(args):
             "TFLOP/s": round(flops / us / 1e6, 1)}
 
 
+def latent_attention(args):
+    """One prompt of --tokens tokens (or --batch decode rows over --context cached tokens with --splits) of
+    latent attention: --heads heads over one cached row of --k elements per token whose first --n are the values."""
+    H, dk, dv = args.heads, args.k, args.n
+    decode = args.tokens <= 1
+    S, new, total = (args.batch, 1, args.context) if decode else (args.seqs, args.tokens, args.tokens)
+    pages_per = (total + 63) // 64
+    cache = (torch.randn(S * pages_per, 1, 64, dk, device=DEV) * 0.5).bfloat16()
+    table = torch.randperm(S * pages_per).to(torch.int32).view(S, pages_per).to(DEV)
+    q = (torch.randn(S * new, H * dk, device=DEV) * 0.5).bfloat16()
+    out = torch.empty(S * new, H * dv, dtype=torch.bfloat16, device=DEV)
+    cu = torch.arange(S + 1, dtype=torch.int32, device=DEV) * new
+    start = torch.full((S,), total - new, dtype=torch.int32, device=DEV)
+    slot = torch.arange(S, dtype=torch.int32, device=DEV)
+    slot_tok = slot.repeat_interleave(new)
+    sinks = torch.zeros(H, device=DEV)
+    splits = args.splits if decode else 1
+    partial = torch.empty(S * new * H * splits * (dv + 2), device=DEV) if splits > 1 else None
+    us = _time(lambda i: ops.latent_attention_mma(q, cache, cu, start, slot, slot_tok, table, out, sinks, new, H, dk, dv, 6,
+                                                  None, dk ** -0.5, splits, partial), args.iters)
+    keys = S * (total if decode else new * (new + 1) / 2)
+    return {"kernel": "latent_attention_mma", "seqs": S, "new": new, "context": total, "heads": H, "dk": dk, "dv": dv,
+            "splits": splits, "us": round(us, 2), "TFLOP/s": round(2.0 * keys * H * (dk + dv) / us / 1e6, 1),
+            "GB/s": round(S * total * dk * 2 / us / 1e3, 1)}
+
+
+def grouped_gemm(args):
+    """The experts' gate/up product with SwiGLU (--kernel swiglu) or a plain one: --tokens tokens, --top of
+    --experts experts each, matrices of --n x --k."""
+    T, top, E, K, N = args.tokens, args.top, args.experts, args.k, args.n
+    expert_of = torch.rand(T, E, device=DEV).argsort(1)[:, :top].int().contiguous()
+    P = T * top
+    mt = ops.expert_tiles_bound(P, E, 64)
+    offsets, order, te, tr, meta = [torch.zeros(n, dtype=torch.int32, device=DEV) for n in (E + 1, P, mt, mt, 1)]
+    ops.group_by_expert(expert_of, E, 64, offsets, order, te, tr, meta)
+    swiglu = args.kernel == "swiglu"
+    x = torch.randn(T, K, device=DEV).bfloat16()
+    w = (torch.randn(E, (2 if swiglu else 1) * N, K, device=DEV) * 0.05).bfloat16()
+    out = torch.empty(P, N, dtype=torch.bfloat16, device=DEV)
+    us = _time(lambda i: ops.grouped_gemm_mma(x, order, top, w, out, None, offsets, te, tr, meta, mt,
+                                              ops.GG_SWIGLU if swiglu else ops.GG_STORE), args.iters)
+    used = E * (1.0 - (1.0 - top / E) ** T)
+    return {"kernel": "grouped_gemm_mma", "swiglu": swiglu, "tokens": T, "top": top, "experts": E, "n": N, "k": K,
+            "us": round(us, 2), "TFLOP/s": round(2.0 * P * w.shape[1] * K / us / 1e6, 1),
+            "GB/s": round(used * w.shape[1] * K * 2 / us / 1e3, 1)}
+
+
+def gated_linear_scan(args):
+    """The recurrence of gated linear attention over one prompt of --tokens tokens: --heads heads with a state of
+    --k x --n, in chunks of --chunk tokens (0: in one go)."""
+    H, d, dv, T = args.heads, args.k, args.n, args.tokens
+    proj = (torch.randn(T, 2 * H * d + H * dv, device=DEV) * 0.5).bfloat16()
+    z, bias = torch.randn(T, H * d, device=DEV), torch.randn(H * d, device=DEV)
+    state = torch.zeros(2, H * d * dv, device=DEV)
+    cu = torch.tensor([0, T], dtype=torch.int32, device=DEV)
+    slots = torch.tensor([1], dtype=torch.int32, device=DEV)
+    out = torch.zeros(T, H * dv, device=DEV)
+    n = -(-T // args.chunk) if args.chunk else 0
+    sums = torch.empty(n * H * d * dv, device=DEV) if n else None
+    decays = torch.empty(n * H * d, device=DEV) if n else None
+    us = _time(lambda i: ops.gated_linear_scan(proj, 0, H * d, 2 * H * d, z, bias, 16.0, d ** -0.5, state, cu, slots, out, H,
+                                               d, dv, chunk=args.chunk, max_new=T, sums=sums, decays=decays), args.iters)
+    return {"kernel": "gated_linear_scan", "tokens": T, "heads": H, "dim": d, "vdim": dv, "chunk": args.chunk,
+            "us": round(us, 2), "float32 GFLOP/s": round(4.0 * T * H * d * dv / us / 1e3, 1)}
+
+
 def sampling(args):
     """The pick of a step: argmax at temperature 0, else a draw under the given cuts.  Eight sets of
     logits in turn (64 rows of 128,256 are 33 MB each)."""
@@ -178,7 +248,8 @@ def sampling(args):
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     sub = ap.add_subparsers(dest="what", required=True)
-    for name in ("attention_decode", "linear", "gemm", "attention_prefill", "sampling"):
+    for name in ("attention_decode", "linear", "gemm", "attention_prefill", "sampling", "latent_attention", "grouped_gemm",
+                 "gated_linear_scan"):
         p = sub.add_parser(name)
         p.add_argument("--iters", type=int, default=20)
         p.add_argument("--heads", type=int, default=32)
@@ -207,6 +278,9 @@ def main(argv=None):
         p.add_argument("--temperature", type=float, default=0.0, help="sampling: 0 is the greedy pick")
         p.add_argument("--top-k", type=int, default=0)
         p.add_argument("--top-p", type=float, default=1.0)
+        p.add_argument("--experts", type=int, default=64)
+        p.add_argument("--top", type=int, default=6)
+        p.add_argument("--chunk", type=int, default=128, help="gated_linear_scan: tokens a chunk (0: in one go)")
     args = ap.parse_args(argv)
     print(json.dumps(globals()[args.what](args)))
 
