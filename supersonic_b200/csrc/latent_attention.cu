@@ -102,9 +102,9 @@ latent_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cac
 
     for (int kb = my_lo; kb <= my_hi; ++kb) {
         const int stage = (kb - my_lo) & 1;
-        if (kb < my_hi) { load_page(kb + 1, stage ^ 1); cp_async_wait<1>(); }
-        else cp_async_wait<0>();
-        __syncthreads();
+        cp_async_wait<0>();
+        __syncthreads();                                              // page kb has landed; everyone is done with kb - 1
+        if (kb < my_hi) load_page(kb + 1, stage ^ 1);                 // ... so its stage and the weights' tile are free
         const uint32_t kbase = (uint32_t)__cvta_generic_to_shared(k_s + stage * LA_BN * ldk);
 
         // scores of this warp's 16 rows on its 16 keys
@@ -201,7 +201,6 @@ latent_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cac
                     mma16816(acc[u][1], l0, l1, l2, l3, b2, b3);
                 }
         }
-        __syncthreads();                                              // the stage and the weights' tile are free
     }
 
 #pragma unroll

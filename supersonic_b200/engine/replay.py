@@ -67,11 +67,13 @@ def main(argv=None) -> int:
     ap.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens live requests hold at any time (each rounded up to 64)")
+                    help="most tokens live requests hold at any time")
     ap.add_argument("--device", type=int, default=0)
     args = ap.parse_args(argv)
+    # the cache hands out whole pages of 64 tokens: room for a partly filled last page of up to 64 live
+    # requests beside the tokens themselves, so that a bound that counts tokens alone is enough
     model = Model.from_dir(args.model, dtype=args.dtype, device=f"cuda:{args.device}",
-                           max_tokens=args.max_tokens)
+                           max_tokens=args.max_tokens + 64 * 64, max_seq_tokens=max(args.max_tokens, 1))
     replayer = Replayer(model, args.out)
     for line in sys.stdin:
         line = line.strip()

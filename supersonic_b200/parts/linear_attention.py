@@ -28,6 +28,10 @@ class GatedLinearAttention:
         self.hidden, self.H = int(params["hidden_size"]), int(params["num_heads"])
         self.dim, self.vdim, self.rank = int(params["dim"]), int(params["value_dim"]), int(params["decay_rank"])
         self.tau, self.eps = float(params["tau"]), float(params["norm_eps"])
+        from ..csrc.ops import SCAN_MAX_DIM
+        if self.dim > SCAN_MAX_DIM:
+            raise ValueError(f"gated linear attention: {self.dim} key channels a head; the recurrence kernel holds up "
+                             f"to {SCAN_MAX_DIM}")
         w, dt = build.weights, build.dtype
         H, d, dv, r = self.H, self.dim, self.vdim, self.rank
         want = {"q": (H * d, self.hidden), "k": (H * d, self.hidden), "v": (H * dv, self.hidden),

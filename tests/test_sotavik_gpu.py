@@ -184,6 +184,33 @@ def test_portions_of_every_size_and_token_by_token(dtype, name):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["R", "S"])
+def test_sizes_that_no_fast_kernel_takes_and_sizes_that_all_take(dtype, name):
+    """Odd widths, ranks and head sizes (every operation on its plain kernel, also in bfloat16) and round ones
+    (every fast kernel, 40 heads over one cached row): a prompt in portions, then decoding, in a batch of two."""
+    from supersonic_b200.engine import StepEntry
+    cfg, store, plain = ts.build(name)
+    model = make_model(cfg, store, dtype)
+    seqs = [tokens_of(cfg, 150, 31), tokens_of(cfg, 70, 32)]
+    refs = [ps.forward(cfg.to_dict(), plain, q) for q in seqs]
+    slots = [model.open_sequence() for _ in seqs]
+    got = [[], []]
+    plan = [((0, 100), (0, 66)), ((100, 130), (66, 68))] + [((130 + i, 131 + i), (68 + i, 69 + i) if i < 2 else None) for i in range(20)]
+    for step in plan:
+        entries = [StepEntry(slots[i], seqs[i][lo_hi[0]:lo_hi[1]], list(range(lo_hi[1] - lo_hi[0])))
+                   for i, lo_hi in enumerate(step) if lo_hi]
+        rows = model.step(entries).cpu().double()
+        at = 0
+        for i, lo_hi in enumerate(step):
+            if lo_hi:
+                got[i].append(rows[at:at + lo_hi[1] - lo_hi[0]])
+                at += lo_hi[1] - lo_hi[0]
+    close(torch.cat(got[0]), refs[0], dtype, name)
+    close(torch.cat(got[1]), refs[1], dtype, name)
+    model.check_errors()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_unequal_batches_against_each_alone_and_reused_slots(dtype):
     """Five requests of 1 to 131 tokens start together and decode together, the short ones ending first;
     then other requests run in the slots and pages those gave back."""

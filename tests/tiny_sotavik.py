@@ -44,7 +44,20 @@ Q = {"architecture": "Sotavik", "vocab": 130, "width": 48, "logit_scale": 1.0, "
                 with_mlp(gla(2, 8, 8, 1.0, 16), None),
                 with_mlp(latent(3, 32, 32, 48, 64), moe(7, 2, 32, 32))]}
 
-CONFIGS = {"P": (P, 11, 0.15), "Q": (Q, 12, 0.2)}
+# sizes that no fast kernel takes (odd widths, ranks and head sizes, one expert of one, top = experts, a rotated
+# part of two coordinates, a decay rank of one) beside ones that all of them take (multiples of 64)
+R = {"architecture": "Sotavik", "vocab": 61, "width": 50, "logit_scale": 1.3, "norm": {"eps": 1e-4},
+     "layers": [with_mlp(latent(3, 10, 6, 7, 21, base=300.0, dims=4), moe(3, 3, 9, 5)),
+                with_mlp(gla(2, 7, 5, 2.5, 1), moe(1, 1, 11)),
+                with_mlp(latent(5, 6, 2, 9, 12, base=50.0), moe(6, 1, 4, 13)),
+                with_mlp(gla(1, 33, 3, 30.0, 3), None)]}
+
+S = {"architecture": "Sotavik", "vocab": 256, "width": 128, "logit_scale": 0.5, "norm": {"eps": 1e-5},
+     "layers": [with_mlp(latent(8, 64, 64, 64, 128), moe(8, 2, 128, 128)),
+                with_mlp(latent(40, 16, 16, 16, 48, dims=8), moe(4, 4, 64)),
+                with_mlp(gla(2, 128, 128, 8.0, 64), moe(16, 2, 64, 256))]}
+
+CONFIGS = {"P": (P, 11, 0.15), "Q": (Q, 12, 0.2), "R": (R, 13, 0.25), "S": (S, 14, 0.1)}
 
 
 def build(name_or_cfg, seed=0, std=0.15):
