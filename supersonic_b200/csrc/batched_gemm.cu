@@ -6,11 +6,13 @@
 // blockIdx.z and blockIdx.y (per-head form), or from the tile list that the grouping kernel wrote
 // (per-expert form: a block whose index is beyond the list's length returns).  Rows of A may be
 // gathered through an index (a_index[r] / a_div) and rows of C scattered through one, so that
-// tokens need not be copied into expert order.  The K range is walked 32 columns a stage through a
-// cp.async ring of two or four stages.  Four (three in flight while one is multiplied) when few rows
-// leave the weights' stream as the only work, which must not wait for each stage in turn: a decode
-// step.  Two when the tiles are full: then what counts is how many blocks an SM holds (seven of
-// 30 KB against three of 61 KB: 2,048 tokens' gate/up of 64 experts 2.6 ms against 3.1 ms).
+// tokens need not be copied into expert order.  The K range is walked through a cp.async ring in one
+// of two forms.  Three stages of 64 columns (two in flight while one is multiplied, 128 bytes of a
+// weight row per request) when few rows leave the weights' stream as the only work, which must not
+// wait for each stage in turn: a decode step (batch 1 of 64 experts: a step 0.65 ms against 0.77 with
+// four stages of 32).  Two stages of 32 columns when the tiles are full: then what counts is how
+// many blocks an SM holds (seven of 30 KB against three of 61 KB: 2,048 tokens' gate/up of 64
+// experts 2.6 ms against 3.1 ms).
 // Epilogues: store (bfloat16 or float32), or SwiGLU: the matrix is [gate rows; up rows] and the
 // tile computes both halves for its columns and stores silu(gate) * up.
 #include "mma_helpers.cuh"
@@ -18,8 +20,7 @@
 
 typedef __nv_bfloat16 bf16;
 
-constexpr int BG_BM = 64, BG_BN = 64, BG_BK = 32;
-constexpr int BG_LD = BG_BK + 8;                 // padded row of a stage in elements: 80 bytes, conflict-free ldmatrix
+constexpr int BG_BM = 64, BG_BN = 64;
 constexpr int BG_THREADS = 128;
 
 struct BgArgs {
@@ -31,9 +32,11 @@ struct BgArgs {
     int up_row0;                                  // SwiGLU: first row of the up half in a matrix
 };
 
-template <bool SWIGLU, typename TC, int BG_STAGES>
+template <bool SWIGLU, typename TC, int BG_STAGES, int BG_BK>
 __global__ void __launch_bounds__(BG_THREADS)
 batched_gemm_kernel(const BgArgs g) {
+    constexpr int BG_LD = BG_BK + 8;          // padded row of a stage: 80 or 144 bytes, conflict-free ldmatrix
+    constexpr int CH = BG_BK / 8;             // 16-byte chunks of a row
     extern __shared__ __align__(16) unsigned char bg_smem[];
     constexpr int A_STAGE = BG_BM * BG_LD, W_STAGE = (SWIGLU ? 2 : 1) * BG_BN * BG_LD;
     bf16* a_s = reinterpret_cast<bf16*>(bg_smem);                    // [stages][A_STAGE]
@@ -63,16 +66,16 @@ batched_gemm_kernel(const BgArgs g) {
     __syncthreads();
     const int K = g.K, N = g.N;
     auto load_stage = [&](int k0, int stage) {
-        // 64 rows x 4 chunks of 8 elements for A, the same for W (twice for SwiGLU)
-        for (int c = tid; c < BG_BM * 4; c += BG_THREADS) {
-            const int r = c >> 2, ch = c & 3, k = k0 + ch * 8;
+        // 64 rows x CH chunks of 8 elements for A, the same for W (twice for SwiGLU)
+        for (int c = tid; c < BG_BM * CH; c += BG_THREADS) {
+            const int r = c / CH, ch = c % CH, k = k0 + ch * 8;
             bf16* dst = a_s + stage * A_STAGE + r * BG_LD + ch * 8;
             const int m = a_rows[r];
             if (m >= 0 && k < K) cp_async16((uint32_t)__cvta_generic_to_shared(dst), A + (size_t)m * g.lda + k);
             else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
         }
-        for (int c = tid; c < (SWIGLU ? 2 : 1) * BG_BN * 4; c += BG_THREADS) {
-            const int r = c >> 2, ch = c & 3, k = k0 + ch * 8;
+        for (int c = tid; c < (SWIGLU ? 2 : 1) * BG_BN * CH; c += BG_THREADS) {
+            const int r = c / CH, ch = c % CH, k = k0 + ch * 8;
             bf16* dst = w_s + stage * W_STAGE + r * BG_LD + ch * 8;
             const int half = r / BG_BN, n = n0 + r % BG_BN;
             if (n < N && k < K) cp_async16((uint32_t)__cvta_generic_to_shared(dst),
@@ -158,17 +161,17 @@ static int bg_launch(const BgArgs& a, int mode, int out_dtype, dim3 grid, int de
     if ((((uintptr_t)a.A | (uintptr_t)a.W) & 15) || ((a.a_batch | a.w_batch) & 7)) return SSB_ERR_BAD_SIZE;
     if (grid.y > 65535 || grid.z > 65535) return SSB_ERR_BAD_SIZE;
     int rc;
-#define SSB_BG_ST(SW, TC, ST) do { \
-        constexpr int smem = ST * (BG_BM + (SW ? 2 : 1) * BG_BN) * BG_LD * 2; \
+#define SSB_BG_ST(SW, TC, ST, BK) do { \
+        constexpr int smem = ST * (BG_BM + (SW ? 2 : 1) * BG_BN) * (BK + 8) * 2; \
         static bool configured = false; \
         if (!configured) { \
-            cudaError_t e = cudaFuncSetAttribute(batched_gemm_kernel<SW, TC, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); \
+            cudaError_t e = cudaFuncSetAttribute(batched_gemm_kernel<SW, TC, ST, BK>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); \
             if (e != cudaSuccess) return (int)e; \
             configured = true; \
         } \
-        rc = ssb_launch(batched_gemm_kernel<SW, TC, ST>, grid, dim3(BG_THREADS), smem, stream, pdl != 0, a); \
+        rc = ssb_launch(batched_gemm_kernel<SW, TC, ST, BK>, grid, dim3(BG_THREADS), smem, stream, pdl != 0, a); \
     } while (0)
-#define SSB_BG(SW, TC) do { if (deep) SSB_BG_ST(SW, TC, 4); else SSB_BG_ST(SW, TC, 2); } while (0)
+#define SSB_BG(SW, TC) do { if (deep) SSB_BG_ST(SW, TC, 3, 64); else SSB_BG_ST(SW, TC, 2, 32); } while (0)
     if (mode == 1 && out_dtype == SSB_BF16) SSB_BG(true, bf16);
     else if (mode == 0 && out_dtype == SSB_BF16) SSB_BG(false, bf16);
     else if (mode == 0 && out_dtype == SSB_F32) SSB_BG(false, float);

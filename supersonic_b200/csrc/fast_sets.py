@@ -316,7 +316,9 @@ class FastKernels(PlainKernels):
                           window, scale)
 
     # ---- latent attention, per-head and per-expert products ---------------------------------------
-    LATENT_SPLIT_BLOCKS = 296      # a decode step cuts its sequences' pages until about two blocks an SM stream them
+    # a decode step cuts its sequences' pages until about one block an SM streams them (16 heads over rows of 576,
+    # 64 x 520 keys: 55 us unsplit, 40 in 2 splits, 49 in 4; 8 x 520: 53, 37, 26, 24 and 22 us in 1, 2, 4, 8 and 16)
+    LATENT_SPLIT_BLOCKS = 148
 
     def head_linear(self, x, w, out):
         if ops.head_gemm_mma_ok(x, w, out):
@@ -345,7 +347,7 @@ class FastKernels(PlainKernels):
             if window:
                 pages = min(pages, (window >> page_shift) + 2)
             blocks = batch.n_seqs * ((n_heads + 31) // 32)
-            splits = max(1, min(self.LATENT_SPLIT_BLOCKS // blocks, pages // 2, 64))
+            splits = max(1, min(self.LATENT_SPLIT_BLOCKS // blocks, pages, 64))
             if splits > 1:
                 partial = self._buffer("latent_partials", batch.n_tokens * n_heads * splits * (kv_rank + 2),
                                        torch.float32, q_abs.device)
