@@ -98,6 +98,10 @@ class SotavikConfig:
             _need(mlp["router"], ("experts", "top"), where + ".mlp.router")
             _positive(mlp["expert"], ("ff",), where + ".mlp.expert")
             _positive(mlp["router"], ("experts", "top"), where + ".mlp.router")
+            for part in ("expert", "shared"):
+                act = (mlp.get(part) or {}).get("act", "silu")
+                if act != "silu":
+                    raise ConfigError(f"{where}.mlp.{part}.act {act!r} is not supported (the design's experts gate with silu)")
             if mlp["router"]["top"] > mlp["router"]["experts"]:
                 raise ConfigError(f"{where}.mlp.router.top exceeds the number of experts")
             if mlp.get("shared"):

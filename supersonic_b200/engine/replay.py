@@ -70,10 +70,11 @@ def main(argv=None) -> int:
                     help="most tokens live requests hold at any time")
     ap.add_argument("--device", type=int, default=0)
     args = ap.parse_args(argv)
-    # the cache hands out whole pages of 64 tokens: room for a partly filled last page of up to 64 live
+    # the cache hands out whole pages of 64 tokens: room for the partly filled last pages of many short live
     # requests beside the tokens themselves, so that a bound that counts tokens alone is enough
     model = Model.from_dir(args.model, dtype=args.dtype, device=f"cuda:{args.device}",
-                           max_tokens=args.max_tokens + 64 * 64, max_seq_tokens=max(args.max_tokens, 1))
+                           max_tokens=args.max_tokens + max(64 * 64, args.max_tokens),
+                           max_seq_tokens=max(args.max_tokens, 1))
     replayer = Replayer(model, args.out)
     for line in sys.stdin:
         line = line.strip()
