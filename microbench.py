@@ -180,10 +180,10 @@ def latent_attention(args):
     splits = args.splits if decode else 1
     partial = torch.empty(S * new * H * splits * (dv + 2), device=DEV) if splits > 1 else None
     us = _time(lambda i: ops.latent_attention_mma(q, cache, cu, start, slot, slot_tok, table, out, sinks, new, H, dk, dv, 6,
-                                                  None, dk ** -0.5, splits, partial), args.iters)
+                                                  None, dk ** -0.5, splits, partial, form=args.form), args.iters)
     keys = S * (total if decode else new * (new + 1) / 2)
     return {"kernel": "latent_attention_mma", "seqs": S, "new": new, "context": total, "heads": H, "dk": dk, "dv": dv,
-            "splits": splits, "us": round(us, 2), "TFLOP/s": round(2.0 * keys * H * (dk + dv) / us / 1e6, 1),
+            "splits": splits, "form": args.form, "us": round(us, 2), "TFLOP/s": round(2.0 * keys * H * (dk + dv) / us / 1e6, 1),
             "GB/s": round(S * total * dk * 2 / us / 1e3, 1)}
 
 
@@ -278,6 +278,7 @@ def main(argv=None):
         p.add_argument("--temperature", type=float, default=0.0, help="sampling: 0 is the greedy pick")
         p.add_argument("--top-k", type=int, default=0)
         p.add_argument("--top-p", type=float, default=1.0)
+        p.add_argument("--form", type=int, default=0, help="latent_attention: warps of a block as 1 x 8, 2 x 4, 2 x 8 (1, 2, 3)")
         p.add_argument("--experts", type=int, default=64)
         p.add_argument("--top", type=int, default=6)
         p.add_argument("--chunk", type=int, default=128, help="gated_linear_scan: tokens a chunk (0: in one go)")

@@ -310,11 +310,13 @@ def latent_attention_mma(q: torch.Tensor, cache: torch.Tensor, cu_new: torch.Ten
                          seq_slot: torch.Tensor, slot_of_token: torch.Tensor, page_table: torch.Tensor,
                          out: torch.Tensor, sinks: Optional[torch.Tensor], max_new: int, n_heads: int, dk: int,
                          dv: int, page_shift: int, window: Optional[int], scale: float, n_splits: int = 1,
-                         partial: Optional[torch.Tensor] = None, pdl: bool = False) -> None:
+                         partial: Optional[torch.Tensor] = None, pdl: bool = False, form: int = 0) -> None:
     """Every head of every new token over its sequence's cached rows [dv values | dk - dv more key elements]
     (``cache`` [pages, 1, 64, dk]); ``q`` [tokens, heads x dk], ``out`` [tokens, heads x dv], both contiguous
     bfloat16.  ``n_splits`` > 1 cuts a sequence's pages into that many parts whose results a second launch
-    merges through ``partial`` (float32, tokens x heads x n_splits x (dv + 2))."""
+    merges through ``partial`` (float32, tokens x heads x n_splits x (dv + 2)).  ``form``: 0 lets the kernel
+    choose how a block's warps are laid out (one group of 16 rows when a sequence brings no more, else two);
+    1, 2, 3 ask for 1 x 8, 2 x 4, 2 x 8 (row groups x slices)."""
     if not latent_attention_mma_ok(q, cache, out, n_heads, dk, dv, page_shift):
         raise KernelError("latent_attention_mma: operands it does not take")
     _need(cu_new, "cu_new", torch.int32, 1); _need(seq_start, "seq_start", torch.int32, 1)
@@ -335,7 +337,7 @@ def latent_attention_mma(q: torch.Tensor, cache: torch.Tensor, cu_new: torch.Ten
         _ptr(q), _ptr(cache), _ptr(cu_new), _ptr(seq_start), _ptr(seq_slot), _ptr(slot_of_token), _ptr(page_table),
         c_int(page_table.shape[1]), _ptr(out), _ptr(partial), _ptr(sinks), c_int(B), c_int(max_new), c_int(T),
         c_int(n_heads), c_int(dk), c_int(dv), c_int(page_shift), c_int(int(window) if window else 0), c_float(scale),
-        c_int(n_splits), c_int(1 if pdl else 0), _stream()), "latent_attention_mma")
+        c_int(n_splits), c_int(form), c_int(1 if pdl else 0), _stream()), "latent_attention_mma")
 
 
 # ---- many small matrix products on the tensor cores -------------------------------------------

@@ -77,12 +77,13 @@ def test_latent_attention_mma_prompts_and_decode(H, dk, dv, window):
         o.attention_plain(q, store, None, batch.pos, batch.slot_of_token, table, plain, H, 1, dk, 6, window, scale,
                           value_dim=dv, sinks=sinks)
         assert float((plain.float() - ref).abs().max()) < 0.02 * max(1.0, float(ref.abs().max()))
-        out = torch.full((T, H * dv), 7.0, dtype=torch.bfloat16, device=DEV)
-        assert o.latent_attention_mma_ok(q, store, out, H, dk, dv, 6)
-        partial = torch.empty(T * H * splits * (dv + 2), device=DEV) if splits > 1 else None
-        o.latent_attention_mma(q, store, batch.cu_new, batch.seq_start, batch.seq_slot, batch.slot_of_token, table, out,
-                               sinks, batch.max_new, H, dk, dv, 6, window, scale, splits, partial)
-        assert float((out.float() - ref).abs().max()) < 0.02 * max(1.0, float(ref.abs().max())), (lengths, new, splits)
+        for form in (0, 1, 2, 3):                                          # every layout of a block's warps
+            out = torch.full((T, H * dv), 7.0, dtype=torch.bfloat16, device=DEV)
+            assert o.latent_attention_mma_ok(q, store, out, H, dk, dv, 6)
+            partial = torch.empty(T * H * splits * (dv + 2), device=DEV) if splits > 1 else None
+            o.latent_attention_mma(q, store, batch.cu_new, batch.seq_start, batch.seq_slot, batch.slot_of_token, table, out,
+                                   sinks, batch.max_new, H, dk, dv, 6, window, scale, splits, partial, form=form)
+            assert float((out.float() - ref).abs().max()) < 0.02 * max(1.0, float(ref.abs().max())), (lengths, new, splits, form)
 
 
 # ---- per-head and per-expert products ---------------------------------------------------------------
