@@ -1,15 +1,16 @@
 """Typed configuration of the ``Sotavik`` architecture.
 
-config.json of this design is nested: ``vocab``, ``width``, ``logit_scale``, ``norm.eps`` and a
-list ``layers`` whose entries name the layer's mixer (``type``: ``latent_attention`` or ``gla``),
-the mixer's sizes (``mixer``) and its feed-forward (``mlp``: experts chosen by a token-id table
-plus an optional shared expert, or null).  Every layer is parallel (one norm with a single gain,
-mixer and feed-forward both read it) and is followed by a learned weighted sum over the results
-of all layers so far.  One size is not in config.json: the inner width of a ``gla`` layer's
-decay projection, which is the shape of its first matrix (``with_shapes`` reads it from the
-stored tensor; a configuration made by hand may give it as ``mixer.decay_rank``).
+Its config.json is nested.  Top level: ``vocab``, ``width``, ``logit_scale``, ``norm.eps`` and ``layers``, a list
+with one entry per layer: ``type`` (``latent_attention`` or ``gla``), ``mixer`` (that mixer's sizes and
+constants) and ``mlp`` (null, or ``{"kind": "moe", "expert": {"ff"}, "router": {"experts", "top"},
+"shared": {"ff"} or null}``).  ``build_spec`` turns that into parts: a ``parallel`` block per layer (a norm
+with a single gain, read by mixer and feed-forward alike) with a depth average behind it, experts routed by
+a token-id table, a head with scaled logits.  Tensor names are ``embed``, ``head``, ``final.norm`` and, per
+layer i, ``l<i>.norm1``, ``l<i>.mix.*``, ``l<i>.mlp.*``, ``l<i>.dwa``.
 
-The design has no position limit of its own; sequences are bounded by the cache.
+One size is not in config.json: the inner width of a ``gla`` layer's decay projection, which is the first
+dimension of ``l<i>.mix.a1`` (``with_shapes`` reads it from the stored tensor; a configuration made by hand
+may give it as ``mixer.decay_rank``).  The design has no position limit; the cache bounds a sequence.
 """
 from __future__ import annotations
 

@@ -1,12 +1,11 @@
 // Latent attention: what lies between the fused projection and the attention itself.
 //
-// A token's projected row holds, head by head, a query of `dim` plain and `rot_dim` rotated
-// coordinates, and after the queries the low-rank key/value row: `kv_rank` latent coordinates and
-// one rotated key part of `rot_dim` that all heads share.  The cache keeps one row per token,
-// [normed latent | rotated key part]; keys and values of the heads are never formed: a head's
-// plain query is carried into the latent space (q' = Wuk_h^T q), scores are
-// q' . latent + q_rot . k_rot over the cached rows, and the weighted sum of latent rows is
-// carried out of it again (Wuv_h).  This file normalises and rotates; all arithmetic is float32.
+// Input: a token's projected row, [H queries of (dim + rot_dim) | kv_rank + rot_dim], the second
+// part being the low-rank row from which keys and values of all H heads derive.  Output: the
+// token's cache row [rms(first kv_rank) * w | rotate(last rot_dim)] at its position, and the
+// rotated rot_dim tails of the H queries behind the latent-space queries in q_abs.  The attention
+// that follows works on these rows directly (see parts/latent_attention.py for the algebra).
+// All arithmetic is float32.
 #include "common.cuh"
 #include <math.h>
 

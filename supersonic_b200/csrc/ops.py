@@ -171,8 +171,8 @@ def attention_plain(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     """Each token attends over keys [max(0, pos-window+1), pos] of its slot in the paged cache.
     ``value_dim``: width of a value and of a head's output when it differs from ``head_dim``;
     ``v_cache`` None: a token's value is the first ``value_dim`` elements of its key row.
-    ``sinks`` (float32, one per query head): one more term exp(sink) in the softmax's denominator,
-    with no key and no value."""
+    ``sinks`` (float32, one per query head): exp(sink) is added to the softmax's denominator and
+    nothing to its numerator."""
     v_dim = head_dim if value_dim is None else int(value_dim)
     v_row = v_dim
     if v_cache is None:

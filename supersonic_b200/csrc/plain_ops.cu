@@ -369,7 +369,7 @@ attention_plain_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k
         m = m_new;
         __syncthreads();
     }
-    // a sink: one more term exp(sink) in the denominator, with no key and no value
+    // a sink adds exp(sink) to the denominator and nothing to the numerator
     float keep = 1.f;
     if (sinks != nullptr) {
         const float sk = sinks[h];

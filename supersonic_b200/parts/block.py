@@ -42,12 +42,12 @@ class ParallelBlock:
     """x <- x + mixer(n) + feed_forward(n), n = norm(x): one norm, read by both sublayers (the
     feed-forward may be absent).
 
-    ``params["depth_average"] = {"index": i, "layers": L}`` adds a weighted sum over depth: with X_0
-    the stream that enters the first layer and X_(j+1) the result of layer j, the stream that leaves
-    layer i is sum_{j <= i+1} w[j] X_j, with the layer's own weights ``depth_weights`` (i + 2 numbers).
-    The results of a step's layers are kept in one float32 stack ``ctx.streams`` [L + 2, T, width]: plane
-    i + 1 holds the stream entering layer i, the sublayers add into it in place (which makes it X_(i+1)),
-    and the weighted sum is written into plane i + 2, which the block returns as the stream from then on.
+    ``params["depth_average"] = {"index": i, "layers": L}`` adds a weighted sum over depth.  Call R_0 what the
+    embedding gives and R_(n+1) = s_n + mixer(norm(s_n)) + feed_forward(norm(s_n)) the raw result of layer n,
+    where s_n is the stream that enters it; then s_(i+1) = sum_{j = 0 .. i+1} a_i[j] R_j with layer i's own
+    i + 2 numbers a_i (``depth_weights``).  The R_j of a step are planes of one float32 stack ``ctx.streams``
+    [L + 2, T, width]: plane i + 1 holds s_i, the sublayers add into it in place (which makes it R_(i+1)), and
+    the weighted sum is written into plane i + 2, which the block returns as the stream from then on.
     """
 
     def __init__(self, mixer, feed_forward, mixer_norm, feed_forward_norm, position, params=None,

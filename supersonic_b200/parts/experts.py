@@ -1,11 +1,11 @@
-"""Feed-forward experts: each token runs ``top`` of ``n_experts`` small gated feed-forwards and adds
-their weighted outputs; an optional shared expert runs for every token and is added too.
+"""Feed-forward experts: y(x) = sum_k w_k E_(e_k)(x) over the ``top`` experts (e_k, w_k) a router picks for the
+token out of ``n_experts``, plus E_shared(x) if the layer has a shared expert.
 
-An expert is down( silu(gate(x)) * up(x) ) without biases.  Which experts a token uses, and with
-what weights, is the router's business; routers are registered by name:
+An expert is a gated unit without biases, E(x) = Wdown (silu(Wgate x) * (Wup x)).  Routers are registered
+by name and fill two arrays per step, the chosen experts and their weights:
 
-* ``table``: no learned router at all.  An integer table [vocab, top] gives every token id its
-  experts (the entries of a row differ); each has weight 1 / top.
+* ``table``: nothing is learned and nothing is computed from x: row ``token id`` of an integer table
+  [vocab, top] names the token's experts (distinct within a row), all with weight 1 / top.
 
 The step's (token, choice) pairs are sorted by expert on the device, the experts' matrix
 products run group by group from that order, and a token's outputs are summed in the order of

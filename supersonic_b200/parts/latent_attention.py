@@ -1,19 +1,21 @@
-"""The latent-attention mixer: softmax attention whose keys and values are carried by one
-low-rank row per token.
+"""The latent-attention mixer: causal softmax attention that caches one low-rank row per token.
 
-With h the normed input: q = Wq h, head by head [dim plain | rot_dim rotated]; Wdkv h gives
-kv_rank + rot_dim numbers: the first kv_rank, RMS-normed with a weight, are the latent c, the
-last rot_dim, rotated by the token's position, are a key part k_r that all heads share.  Head
-g's key is [Wuk_g c | k_r] and its value Wuv_g c; the score of query t on key j is
-(q_plain . Wuk_g c_j + q_rot . k_r,j) * scale, causal, and the softmax may carry a sink: one
-more term exp(sink_g) in the denominator that has no key and no value.
+In equations, for a token at position p with normed input h, per head g of H:
 
-Only [c | k_r] is cached (one row per token, whatever the number of heads), and the keys and
-values are never formed: q_plain is carried into the latent space once per query,
-q' = Wuk_g^T q_plain, so that the score is q' . c_j + q_rot . k_r,j; the weighted sum of the
-c_j is taken in the latent space and Wuv_g is applied to that sum.  Per cached token a head
-then costs kv_rank + rot_dim multiply-adds for the score and kv_rank for the value, with no
-per-token matrix product.
+    u_g = Wq_g h                       split as u_g = [a_g (dim) | b_g (rot_dim)]
+    y   = Wdkv h                       split as y   = [y_lat (kv_rank) | y_rot (rot_dim)]
+    c   = rms(y_lat) * w_norm          the latent row of the token
+    r   = rot_p(y_rot),  b'_g = rot_p(b_g)      rotation by the position encoding the mixer is given
+    K_g(j) = [Wuk_g c_j | r_j],   V_g(j) = Wuv_g c_j          for every earlier or equal position j
+    s_gj = ([a_g | b'_g] . K_g(j)) * scale
+    out_g = sum_j exp(s_gj) V_g(j) / (sum_j exp(s_gj) + exp(sink_g))       (without a sink: the plain softmax)
+    result = Wo [out_1 ... out_H]
+
+The cache holds [c_j | r_j] per token, whatever H is.  K and V are never formed: since
+a_g . (Wuk_g c_j) = (Wuk_g^T a_g) . c_j, the query is moved into the latent space once
+(a'_g = Wuk_g^T a_g), the score is a'_g . c_j + b'_g . r_j, the probabilities weight the c_j
+themselves, and Wuv_g is applied to that one sum per query.  A cached token then costs a head
+2 kv_rank + rot_dim multiply-adds and no matrix product.
 """
 from __future__ import annotations
 

@@ -1,13 +1,18 @@
 """Gated linear attention: a mixer whose memory is a matrix per head instead of a list of keys.
 
-With h the normed input: q = Wq h * dim^(-1/2), k = Wk h (heads x dim), v = Wv h (heads x vdim),
-and a decay per key channel a = sigmoid(z)^(1/tau), z = Wa2 (Wa1 h) + b (a low-rank projection).
-Per head, token after token:  S <- diag(a) S + k v^T,  o = S^T q.  Each head's o is RMS-normed
-over its vdim with one weight vector, multiplied by silu(Wg h), and the heads are projected by Wo.
+In equations, for token t with normed input h, per head g (key width dim, value width vdim):
 
-S (dim x vdim float32 per head) is the sequence's state: it starts at zero, lives in the cache's
-fixed-size state rows and is carried from step to step.  z, the decay, the state and o are
-float32 whatever the activation type; the projections run in the activation type.
+    q = (Wq_g h) / sqrt(dim),   k = Wk_g h,   v = Wv_g h
+    z = Wa2 (Wa1 h) + b                          a low-rank projection, one number per head and key channel
+    a = sigmoid(z) ** (1 / tau)                  decay in (0, 1) per key channel
+    S_t = diag(a) S_(t-1) + k v^T                S_0 = 0, shape [dim, vdim]
+    o = S_t^T q
+    y_g = rms(o) * w_norm * silu(Wg_g h)         w_norm [vdim] is the same vector for every head
+    result = Wo [y_1 ... y_H]
+
+S is the sequence's state: it lives in the cache's fixed-size float32 rows and is carried from
+step to step.  z, the decays, the state and o are float32 whatever the activation type; the
+matrix products run in the activation type.
 """
 from __future__ import annotations
 
