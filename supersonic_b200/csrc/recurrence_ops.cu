@@ -91,12 +91,19 @@ gated_linear_scan_kernel(const T* __restrict__ proj, int ld, int q_off, int k_of
     for (int e = tid; e < 3 * SCAN_TOKENS * dimp; e += NT) sm[e] = 0.f;      // the padding stays zero
     // a turn stages SCAN_TOKENS tokens: item (token, channel) n * NT + tid of the turn is this thread's
     float zz[SCAN_ITEMS], kk[SCAN_ITEMS], qq[SCAN_ITEMS], vv = 0.f, a_prod = 1.f;
+    int item_tt[SCAN_ITEMS], item_i[SCAN_ITEMS];         // the same in every turn: divided once
+#pragma unroll
+    for (int n = 0; n < SCAN_ITEMS; ++n) {
+        const int item = n * NT + tid;
+        item_tt[n] = item < SCAN_TOKENS * dim ? item / dim : SCAN_TOKENS;
+        item_i[n] = item % dim;
+    }
     auto fetch = [&](int t) {
         const int n_tok = min(SCAN_TOKENS, t1 - t);
 #pragma unroll
         for (int n = 0; n < SCAN_ITEMS; ++n) {
-            const int item = n * NT + tid, tt = item / dim, i = item % dim;
-            if (item < SCAN_TOKENS * dim && tt < n_tok) {
+            const int tt = item_tt[n], i = item_i[n];
+            if (tt < n_tok) {
                 const T* row = proj + (size_t)(t + tt) * ld;
                 zz[n] = z[(size_t)(t + tt) * ldz + h * dim + i];
                 kk[n] = ssb_to_float(row[k_off + h * dim + i]);
@@ -114,8 +121,8 @@ gated_linear_scan_kernel(const T* __restrict__ proj, int ld, int q_off, int k_of
         const int n_tok = min(SCAN_TOKENS, t1 - t);
 #pragma unroll
         for (int n = 0; n < SCAN_ITEMS; ++n) {
-            const int item = n * NT + tid, tt = item / dim, i = item % dim;
-            if (item < SCAN_TOKENS * dim && tt < n_tok) {
+            const int tt = item_tt[n], i = item_i[n];
+            if (tt < n_tok) {
                 a_s[tt * dimp + i] = zz[n];
                 k_s[tt * dimp + i] = kk[n];
                 q_s[tt * dimp + i] = qq[n] * q_scale;
