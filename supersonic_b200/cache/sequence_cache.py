@@ -44,10 +44,31 @@ class KvNeed:
 
 @dataclass(frozen=True)
 class StateNeed:
-    n_values: int                      # float32 values per sequence
+    n_values: int                      # values per sequence
+    kind: str = "float32"              # "float32", or "int32" for a row of integers (a remembered token id)
 
 
 Need = Union[KvNeed, StateNeed]
+_STATE_DTYPES = {"float32": torch.float32, "int32": torch.int32}
+
+
+def flatten_needs(needs) -> Dict[object, Need]:
+    """One entry per store.  A part that needs several things says so with a dictionary
+    ``{name: need}`` (nested ones too); the store of ``name`` under cache id ``c`` then has the key
+    ``(c, name)``, which is what the part asks ``kv()`` / ``state()`` for."""
+    flat: Dict[object, Need] = {}
+
+    def walk(key, need):
+        if need is None:
+            return
+        if isinstance(need, dict):
+            for name, sub in need.items():
+                walk((key, name), sub)
+        else:
+            flat[key] = need
+    for cid, need in needs.items():
+        walk(cid, need)
+    return flat
 
 
 def pages_for(n_tokens: int) -> int:
@@ -156,14 +177,17 @@ class SequenceCache:
         # tables and other per-position data of the parts are sized by it
         self.max_seq_tokens = min(int(max_seq_tokens), self.pages_per_seq * PAGE_TOKENS)
         self.max_slots = max_slots if max_slots is not None else min(self.n_pages, 4096)
+        needs = flatten_needs(needs)
         self._preflight(needs, max_tokens, max_seq_tokens)
         # groups by need
         by_need: Dict[KvNeed, List[int]] = {}
         state_entries: List[Tuple[int, StateNeed]] = []
-        for cid, need in sorted(needs.items()):
+        for cid, need in needs.items():
             if isinstance(need, KvNeed):
                 by_need.setdefault(need, []).append(cid)
             elif isinstance(need, StateNeed):
+                if need.kind not in _STATE_DTYPES:
+                    raise CacheError(f"cache entry {cid}: state of kind {need.kind!r} (known: {sorted(_STATE_DTYPES)})")
                 state_entries.append((cid, need))
             elif need is not None:
                 raise CacheError(f"cache entry {cid}: unknown need {need!r}")
@@ -178,7 +202,7 @@ class SequenceCache:
         self.slots = _Slots(self._book, self.max_slots)
         self._group_of: Dict[int, KvGroup] = {e: g for g in self.kv_groups for e in g.entries}
         self._state: Dict[int, torch.Tensor] = {
-            cid: torch.zeros((self.max_slots, need.n_values), dtype=torch.float32, device=device)
+            cid: torch.zeros((self.max_slots, need.n_values), dtype=_STATE_DTYPES[need.kind], device=device)
             for cid, need in state_entries}
         self.rng_state = torch.zeros(self.max_slots, dtype=torch.int64, device=device)
 
@@ -193,7 +217,7 @@ class SequenceCache:
         item = torch.empty((), dtype=dtype).element_size()
         total = slots * 8                                                  # generator state
         seen = set()
-        for need in needs.values():
+        for need in flatten_needs(needs).values():
             if isinstance(need, KvNeed):
                 total += n_pages * need.n_kv_heads * PAGE_TOKENS * (need.head_dim + need.v_dim) * item
                 if need not in seen:                                       # one page table a group
@@ -279,7 +303,7 @@ class SequenceCache:
         return g.k[i], g.v[i], g.table, g
 
     def state(self, cache_id: int) -> torch.Tensor:
-        """Fixed-size state ``[slots, n_values]`` float32 of one cache entry."""
+        """Fixed-size state ``[slots, n_values]`` of one cache entry (float32, or int32 if the need says so)."""
         return self._state[cache_id]
 
     def free_tokens(self) -> int:

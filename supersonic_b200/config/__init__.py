@@ -3,11 +3,12 @@ from .base import (BlockSpec, ConfigError, ModelSpec, PartSpec, ScheduleEntry,
                    default_schedule)
 from .llama import LlamaConfig, RopeScaling
 from .sotavik import SotavikConfig
+from .vufadra import VufadraConfig
 from .registry import (config_from_dict, known_architectures, load_config,
                        lookup_architecture, preset_config, preset_names,
                        register_architecture, spec_from_config)
 
 __all__ = ["BlockSpec", "ConfigError", "ModelSpec", "PartSpec", "ScheduleEntry",
-           "default_schedule", "LlamaConfig", "RopeScaling", "SotavikConfig", "config_from_dict",
+           "default_schedule", "LlamaConfig", "RopeScaling", "SotavikConfig", "VufadraConfig", "config_from_dict",
            "known_architectures", "load_config", "lookup_architecture", "preset_config",
            "preset_names", "register_architecture", "spec_from_config"]

@@ -13,7 +13,7 @@ per-layer choice is first-class data instead.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Dict, List, Optional
+from typing import Any, Dict, List, Optional, Tuple
 
 
 class ConfigError(ValueError):
@@ -56,11 +56,15 @@ class ScheduleEntry:
     the mixer reads; two stops with the same ``cache`` share storage.
     ``writes_cache`` is False for a stop that only reads what an earlier stop
     of the same step wrote (a layer that borrows another layer's keys).
+    ``before = (adapter, pass)``: stream adapter ``ModelSpec.adapters[adapter]`` acts on the stream
+    before the stop's block, and is told the number of the pass (a run of layers walked several
+    times enters each pass through one).
     """
 
     layer: int
     cache: int
     writes_cache: bool = True
+    before: Optional[Tuple[int, int]] = None
 
 
 @dataclass(frozen=True)
@@ -75,6 +79,7 @@ class ModelSpec:
     final_norm: PartSpec
     head: PartSpec
     stop_token_ids: List[int] = field(default_factory=list)
+    adapters: List[PartSpec] = field(default_factory=list)    # stream adapters the schedule's stops may name
 
     def validate(self) -> None:
         if not self.blocks:
@@ -84,6 +89,9 @@ class ModelSpec:
             if not 0 <= stop.layer < len(self.blocks):
                 raise ConfigError(f"schedule[{i}] names layer {stop.layer}, "
                                   f"but there are {len(self.blocks)} blocks")
+            if stop.before is not None and not 0 <= stop.before[0] < len(self.adapters):
+                raise ConfigError(f"schedule[{i}] names stream adapter {stop.before[0]}, "
+                                  f"but there are {len(self.adapters)}")
             if stop.writes_cache:
                 written.add(stop.cache)
             elif stop.cache not in written:

@@ -47,6 +47,8 @@ LIBRARIES: Dict[str, Dict[str, List[str]]] = {
     "latent_ops": {"sources": ["latent_ops.cu"], "flags": [], "link": []},
     "recurrence_ops": {"sources": ["recurrence_ops.cu"], "flags": [], "link": []},
     "expert_ops": {"sources": ["expert_ops.cu"], "flags": [], "link": []},
+    "sequence_ops": {"sources": ["sequence_ops.cu"], "flags": [], "link": []},
+    "gated_attention": {"sources": ["gated_attention.cu"], "flags": [], "link": []},
     "random_fill": {"sources": ["random_fill.cu"], "flags": [], "link": []},
     # the host side's native core: no CUDA in it, so it is compiled by the C++ compiler alone
     "host_runtime": {"sources": ["runtime.cpp"], "flags": [], "link": [], "dir": os.path.join(os.path.dirname(_HERE), "host"),

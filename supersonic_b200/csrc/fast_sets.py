@@ -366,9 +366,6 @@ class FastKernels(PlainKernels):
                               batch.seq_slot, out, n_heads, dim, vdim, pdl=self.pdl, chunk=chunk,
                               max_new=batch.max_new, sums=sums, decays=decays)
 
-    def head_norm_gate(self, o, weight, eps, gate, out, n_heads, vdim):
-        ops.head_norm_gate(o, weight, eps, gate, out, n_heads, vdim, pdl=self.pdl)
-
     def route_table(self, token_ids, table, n_experts, expert_of, pair_weight):
         ops.route_table(token_ids, table, n_experts, expert_of, pair_weight, pdl=self.pdl)
 

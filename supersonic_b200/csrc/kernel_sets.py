@@ -54,6 +54,7 @@ def as_tensor(x) -> torch.Tensor:
 class PlainKernels:
     name = "plain"
     capturable = False      # the float32 path launches every step eagerly: each launch's status is looked at
+    pdl = False             # no launch is a programmatic dependent of the one before
 
     def embed(self, ids, table, out):
         ops.embed(ids, table, out)
@@ -134,8 +135,68 @@ class PlainKernels:
                               batch.seq_slot, out, n_heads, dim, vdim, chunk=chunk, max_new=batch.max_new,
                               sums=sums, decays=decays)
 
-    def head_norm_gate(self, o, weight, eps, gate, out, n_heads, vdim):
-        ops.head_norm_gate(o, weight, eps, gate, out, n_heads, vdim)
+    def head_norm_gate(self, o, weight, eps, gate, out, n_heads, vdim, gate_kind="silu"):
+        ops.head_norm_gate(o, weight, eps, gate, out, n_heads, vdim, pdl=self.pdl, gate_kind=gate_kind)
+
+    def state_scan_prepare(self, z, z_bias, decay_kind, decay_scale, n_heads, dim, proj=None, k_off=0, a_off=0,
+                           a_bias=None, unit_eps=0.0, unit=None):
+        """The float32 inputs of a matrix-state recurrence: decays in place of ``z``; unit keys and removal
+        vectors into ``unit`` (see ``ops.state_scan_prepare``)."""
+        ops.state_scan_prepare(z, z_bias, decay_kind, decay_scale, n_heads, dim, proj, k_off, a_off, a_bias, unit_eps,
+                               unit, pdl=self.pdl)
+
+    def matrix_state_scan(self, proj, r_off, k_off, v_off, decay, kind, state, batch, out, n_heads, dim, vdim,
+                          unit=None, bonus=None):
+        """``kind`` ``"delta"`` (decay, removal along the unit key, then the new pair) or ``"bonus"`` (decay, with
+        the token at hand read through a bonus), over every sequence's new tokens from and into its state."""
+        ops.matrix_state_scan(proj, r_off, k_off, v_off, decay, kind, state, batch.cu_new, batch.seq_slot, out,
+                              n_heads, dim, vdim, unit=unit, bonus=bonus, pdl=self.pdl)
+
+    def gated_unit_scan(self, gates, bias_r, bias_i, rate, u, y, y_bias, state, batch, out, block):
+        ops.gated_unit_scan(gates, bias_r, bias_i, rate, u, y, y_bias, state, batch.cu_new, batch.seq_slot, out, block,
+                            pdl=self.pdl)
+
+    # ---- along a sequence --------------------------------------------------------------
+    def pair_embed(self, ids, table, pair, prev, batch, out, buckets, mul_prev, mul_cur):
+        ops.pair_embed(ids, table, pair, prev, batch.cu_new, batch.seq_slot, out, batch.max_new, buckets, mul_prev,
+                       mul_cur, pdl=self.pdl)
+
+    def dynamic_tanh(self, x, alpha, weight, bias, out, rows=None):
+        ops.dynamic_tanh(x, alpha, weight, bias, out, rows, pdl=self.pdl and out.shape[0] <= 64)
+
+    def shift_mix(self, h, mu, last, batch, out):
+        """out[s] = h + (h shifted by one token - h) * mu[s]; ``last`` carries a sequence's last row across steps."""
+        ops.shift_mix(h, mu, last, batch.cu_new, batch.seq_slot, out, batch.max_new, pdl=self.pdl)
+
+    def causal_conv(self, x, x_bias, weight, bias, tail, batch, out):
+        ops.causal_conv(x, x_bias, weight, bias, tail, batch.cu_new, batch.seq_slot, out, batch.max_new, pdl=self.pdl)
+
+    def concat_cast(self, x, x0, act, bias, out):
+        ops.concat_cast(x, x0, act, bias, out, pdl=self.pdl)
+
+    def rms_pair_add(self, residual, a, wa, b, wb, eps, scale):
+        ops.rms_pair_add(residual, a, wa, b, wb, eps, scale, pdl=self.pdl)
+
+    def tanh_(self, x):
+        ops.tanh_(x, pdl=self.pdl)
+
+    # ---- attention with sigmoid weights --------------------------------------------------
+    def qk_norm_rope_append(self, qkv, q_weight, k_weight, eps, position, kv, batch, n_q, n_kv, dim, vdim, page_shift,
+                            write_cache=True):
+        """Per-head RMS norm of q and k, rotation of their first coordinates, k and v into the cache."""
+        cos = sin = None
+        rot_dims = 0
+        if position is not None:
+            position.check_range(batch)
+            cos, sin, rot_dims = position.rotary_tables()
+        k_cache, v_cache, table, _ = kv
+        ops.qk_norm_rope_append(qkv, q_weight, k_weight, eps, cos, sin, batch.pos, batch.slot_of_token, table, k_cache,
+                                v_cache, n_q, n_kv, dim, vdim, rot_dims, page_shift, write_cache, pdl=self.pdl)
+
+    def sigmoid_attention(self, q, k_cache, v_cache, batch, page_table, bias, out, n_q, n_kv, dim, vdim, page_shift,
+                          chunk, window, scale):
+        ops.sigmoid_attention_plain(q, k_cache, v_cache, batch.pos, batch.slot_of_token, page_table, bias, out, n_q,
+                                    n_kv, dim, vdim, page_shift, chunk, window, scale, pdl=self.pdl)
 
     # ---- experts ---------------------------------------------------------------------
     expert_tile_rows = 64

@@ -456,19 +456,291 @@ def scan_chunking(n_seqs: int, max_new: int, n_heads: int, dim: int, vdim: int):
 
 
 def head_norm_gate(o: torch.Tensor, weight: torch.Tensor, eps: float, gate: torch.Tensor, out: torch.Tensor,
-                   n_heads: int, vdim: int, pdl: bool = False) -> None:
-    """out[t, h] = o[t, h] / sqrt(mean(o[t, h]^2) + eps) * weight * silu(gate[t, h]): every head's ``vdim``
-    outputs normalised on their own with one weight vector, then gated.  ``o`` float32."""
+                   n_heads: int, vdim: int, pdl: bool = False, gate_kind: str = "silu") -> None:
+    """out[t, h] = o[t, h] / sqrt(mean(o[t, h]^2) + eps) * weight * act(gate[t, h]): every head's ``vdim``
+    outputs normalised on their own, weighted (``weight`` [vdim]: one vector for all heads; [heads x vdim]: one
+    per head), then gated; ``gate_kind``: ``"silu"``, ``"sigmoid"`` or ``"none"`` (the gate as given).  ``o`` float32."""
     _need(o, "o", torch.float32, 2); _need(weight, "weight", None, 1); _need(gate, "gate", None, 2)
     _need(out, "out", gate.dtype, 2)
     T = o.shape[0]
     if gate.shape[0] != T or out.shape[0] != T or min(o.shape[1], gate.shape[1], out.shape[1]) < n_heads * vdim \
-            or weight.shape[0] != vdim:
+            or weight.shape[0] not in (vdim, n_heads * vdim) or not weight.is_contiguous():
         raise KernelError("head_norm_gate: sizes")
+    w_stride = vdim if weight.shape[0] == n_heads * vdim and n_heads > 1 else 0
     _check(_fn("recurrence_ops", "ssb_head_norm_gate")(
-        _ptr(o), c_int(o.stride(0)), _ptr(weight), c_int(dtype_code(weight.dtype)), c_float(eps), _ptr(gate),
-        c_int(gate.stride(0)), _ptr(out), c_int(out.stride(0)), c_int(dtype_code(out.dtype)), c_int(T),
-        c_int(n_heads), c_int(vdim), c_int(1 if pdl else 0), _stream()), "head_norm_gate")
+        _ptr(o), c_int(o.stride(0)), _ptr(weight), c_int(dtype_code(weight.dtype)), c_int(w_stride), c_float(eps),
+        _ptr(gate), c_int(gate.stride(0)), c_int(GATE_KINDS[gate_kind]), _ptr(out), c_int(out.stride(0)),
+        c_int(dtype_code(out.dtype)), c_int(T), c_int(n_heads), c_int(vdim), c_int(1 if pdl else 0), _stream()),
+        "head_norm_gate")
+
+
+GATE_KINDS = {"silu": 0, "sigmoid": 1, "none": 2}
+DECAY_KINDS = {"double_exp": 0, "exp_sigmoid": 1}
+STATE_SCAN_KINDS = {"delta": 0, "bonus": 1}
+
+
+def state_scan_prepare(z: torch.Tensor, z_bias: torch.Tensor, decay_kind: str, decay_scale: float, n_heads: int,
+                       dim: int, proj: Optional[torch.Tensor] = None, k_off: int = 0, a_off: int = 0,
+                       a_bias: Optional[torch.Tensor] = None, unit_eps: float = 0.0,
+                       unit: Optional[torch.Tensor] = None, pdl: bool = False) -> None:
+    """What a matrix-state recurrence reads besides its projections, in float32.  ``z`` [T, heads x dim] is
+    overwritten with the decays: ``"double_exp"``: exp(-exp(z + z_bias)); ``"exp_sigmoid"``:
+    exp(-decay_scale * sigmoid(z + z_bias)).  With ``unit`` [T, 2 x heads x dim]: its first half gets the unit keys
+    u = k / sqrt(sum_head(k^2) + unit_eps), its second half a * u with a = sigmoid(proj[a_off ..] + a_bias);
+    k and the removal's pre-activation are columns of ``proj``."""
+    _need(z, "z", torch.float32, 2); _need(z_bias, "z_bias", torch.float32, 1)
+    T, HD = z.shape[0], n_heads * dim
+    if z.shape[1] < HD or z_bias.shape[0] != HD:
+        raise KernelError("state_scan_prepare: sizes")
+    ld = ldu = 0
+    dt = F32
+    if unit is not None:
+        _need(unit, "unit", torch.float32, 2); _need(proj, "proj", None, 2); _need(a_bias, "a_bias", torch.float32, 1)
+        if unit.shape[0] != T or unit.shape[1] < 2 * HD or proj.shape[0] != T or max(k_off, a_off) + HD > proj.shape[1] \
+                or a_bias.shape[0] != HD:
+            raise KernelError("state_scan_prepare: sizes of the unit keys")
+        ld, ldu, dt = proj.stride(0), unit.stride(0), dtype_code(proj.dtype)
+    _check(_fn("recurrence_ops", "ssb_state_scan_prepare")(
+        _ptr(z), c_int(z.stride(0)), _ptr(z_bias), c_int(DECAY_KINDS[decay_kind]), c_float(decay_scale),
+        _ptr(proj if unit is not None else None), c_int(ld), c_int(dt), c_int(k_off), c_int(a_off),
+        _ptr(a_bias if unit is not None else None), c_float(unit_eps), _ptr(unit), c_int(ldu), c_int(T), c_int(n_heads),
+        c_int(dim), c_int(1 if pdl else 0), _stream()), "state_scan_prepare")
+
+
+def matrix_state_scan(proj: torch.Tensor, r_off: int, k_off: int, v_off: int, decay: torch.Tensor, kind: str,
+                      state: torch.Tensor, cu_new: torch.Tensor, seq_slot: torch.Tensor, out: torch.Tensor,
+                      n_heads: int, dim: int, vdim: int, unit: Optional[torch.Tensor] = None,
+                      bonus: Optional[torch.Tensor] = None, pdl: bool = False) -> None:
+    """Per sequence and head over the sequence's new tokens in order, S [dim, vdim] float32 read from and left in
+    ``state[slot]``.  ``"delta"``: S = diag(w) S - (a u)(u^T S) + k v^T, out = S^T r, with ``unit`` = [u | a u] as
+    ``state_scan_prepare`` leaves it; ``"bonus"``: out = (S + diag(bonus) k v^T)^T r, then S = diag(w) S + k v^T.
+    ``decay`` [T, heads x dim] float32 holds w; r, k (heads x dim) and v (heads x vdim) are columns of ``proj``."""
+    _need(proj, "proj", None, 2); _need(decay, "decay", torch.float32, 2); _need(state, "state", torch.float32, 2)
+    _need(out, "out", torch.float32, 2); _need(cu_new, "cu_new", torch.int32, 1); _need(seq_slot, "seq_slot", torch.int32, 1)
+    T, B, HD = proj.shape[0], seq_slot.shape[0], n_heads * dim
+    if decay.shape[0] != T or out.shape[0] != T or decay.shape[1] < HD or out.shape[1] < n_heads * vdim \
+            or cu_new.shape[0] != B + 1 or max(r_off, k_off) + HD > proj.shape[1] or v_off + n_heads * vdim > proj.shape[1]:
+        raise KernelError("matrix_state_scan: sizes")
+    if state.shape[1] != HD * vdim or not state.is_contiguous() or dim > SCAN_MAX_DIM:
+        raise KernelError(f"matrix_state_scan: state rows of heads x dim x vdim, dim up to {SCAN_MAX_DIM}")
+    if kind == "delta":
+        _need(unit, "unit", torch.float32, 2)
+        if unit.shape[0] != T or unit.shape[1] < 2 * HD:
+            raise KernelError("matrix_state_scan: unit keys")
+    if bonus is not None:
+        _need(bonus, "bonus", torch.float32)
+        if bonus.numel() != HD or not bonus.is_contiguous():
+            raise KernelError("matrix_state_scan: one bonus per head and key channel")
+    _check(_fn("recurrence_ops", "ssb_matrix_state_scan")(
+        _ptr(proj), c_int(proj.stride(0)), c_int(dtype_code(proj.dtype)), c_int(r_off), c_int(k_off), c_int(v_off),
+        _ptr(decay), c_int(decay.stride(0)), c_int(STATE_SCAN_KINDS[kind]), _ptr(unit),
+        c_int(unit.stride(0) if unit is not None else 0), _ptr(bonus), _ptr(state), _ptr(cu_new), _ptr(seq_slot),
+        _ptr(out), c_int(out.stride(0)), c_int(B), c_int(n_heads), c_int(dim), c_int(vdim), c_int(1 if pdl else 0),
+        _stream()), "matrix_state_scan")
+
+
+def gated_unit_scan(gates: torch.Tensor, bias_r: torch.Tensor, bias_i: torch.Tensor, rate: torch.Tensor,
+                    u: torch.Tensor, y: torch.Tensor, y_bias: Optional[torch.Tensor], state: torch.Tensor,
+                    cu_new: torch.Tensor, seq_slot: torch.Tensor, out: torch.Tensor, block: int,
+                    pdl: bool = False) -> None:
+    """Per sequence and channel over the new tokens: r = sigmoid(g_r + bias_r), i = sigmoid(g_i + bias_i),
+    a = exp(rate * r), S = a S + sqrt(1 - a^2) i u, out = S * gelu_tanh(y + y_bias).  ``gates`` [T, 2 x channels]
+    float32 holds [g_r | g_i] per block of ``block`` channels; S float32 lives in ``state[slot]``."""
+    _need(gates, "gates", torch.float32, 2); _need(u, "u", None, 2); _need(y, "y", u.dtype, 2); _need(out, "out", u.dtype, 2)
+    _need(state, "state", torch.float32, 2)
+    C = state.shape[1]
+    for name, v in (("bias_r", bias_r), ("bias_i", bias_i), ("rate", rate)) + ((("y_bias", y_bias),) if y_bias is not None else ()):
+        _need(v, name, torch.float32, 1)
+        if v.shape[0] != C:
+            raise KernelError(f"gated_unit_scan: {name} must have one value per channel")
+    T, B = u.shape[0], seq_slot.shape[0]
+    if gates.shape[0] != T or gates.shape[1] < 2 * C or min(u.shape[1], y.shape[1], out.shape[1]) < C or y.shape[0] != T \
+            or out.shape[0] != T or cu_new.shape[0] != B + 1 or C % block or not state.is_contiguous():
+        raise KernelError("gated_unit_scan: sizes")
+    _check(_fn("recurrence_ops", "ssb_gated_unit_scan")(
+        _ptr(gates), c_int(gates.stride(0)), _ptr(bias_r), _ptr(bias_i), _ptr(rate), _ptr(u), c_int(u.stride(0)),
+        _ptr(y), c_int(y.stride(0)), _ptr(y_bias), _ptr(state), _ptr(cu_new), _ptr(seq_slot), _ptr(out),
+        c_int(out.stride(0)), c_int(dtype_code(u.dtype)), c_int(B), c_int(C), c_int(block), c_int(1 if pdl else 0),
+        _stream()), "gated_unit_scan")
+
+
+# ---- operations along a sequence -----------------------------------------------------------
+def pair_embed(ids: torch.Tensor, table: torch.Tensor, pair: torch.Tensor, prev: torch.Tensor, cu_new: torch.Tensor,
+               seq_slot: torch.Tensor, out: torch.Tensor, max_new: int, buckets: int, mul_prev: int, mul_cur: int,
+               pdl: bool = False) -> None:
+    """out[t] = table[id_t] + pair[(id_(t-1) * mul_prev + id_t * mul_cur) mod buckets], row ``buckets`` of ``pair`` for
+    a sequence's first token; ``prev`` [slots, 1] int32 keeps a sequence's last token id + 1 (0: none yet)."""
+    _need(ids, "ids", torch.int32, 1); _need(table, "table", None, 2); _need(pair, "pair", table.dtype, 2)
+    _need(prev, "prev", torch.int32, 2); _need(out, "out", torch.float32, 2)
+    if not (table.is_contiguous() and pair.is_contiguous() and out.is_contiguous() and prev.is_contiguous()) \
+            or prev.shape[1] != 1 or pair.shape[0] != buckets + 1 or pair.shape[1] != table.shape[1] \
+            or tuple(out.shape) != (ids.shape[0], table.shape[1]) or cu_new.shape[0] != seq_slot.shape[0] + 1:
+        raise KernelError("pair_embed: shapes")
+    _check(_fn("sequence_ops", "ssb_pair_embed")(
+        _ptr(ids), _ptr(table), _ptr(pair), c_int(dtype_code(table.dtype)), _ptr(prev), _ptr(cu_new), _ptr(seq_slot),
+        _ptr(out), c_int(seq_slot.shape[0]), c_int(max_new), c_int(table.shape[1]), c_int(table.shape[0]),
+        c_int(buckets), c_longlong(mul_prev), c_longlong(mul_cur), c_int(1 if pdl else 0), _stream()), "pair_embed")
+
+
+def dynamic_tanh(x: torch.Tensor, alpha: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, out: torch.Tensor,
+                 rows: Optional[torch.Tensor] = None, pdl: bool = False) -> None:
+    """out[r] = tanh(alpha * x[rows[r] or r]) * weight + bias; x, alpha [1], weight and bias float32."""
+    _need(x, "x", torch.float32, 2); _need(alpha, "alpha", torch.float32, 1); _need(weight, "weight", torch.float32, 1)
+    _need(bias, "bias", torch.float32, 1); _need(out, "out", None, 2)
+    n, width = out.shape[0], x.shape[1]
+    if not (x.is_contiguous() and out.is_contiguous()) or out.shape[1] != width or weight.shape[0] != width \
+            or bias.shape[0] != width or alpha.numel() != 1 or (rows is None and x.shape[0] != n):
+        raise KernelError("dynamic_tanh: shapes")
+    if rows is not None:
+        _need(rows, "rows", torch.int32, 1)
+        if rows.shape[0] != n:
+            raise KernelError("dynamic_tanh: one output row per gathered row")
+    _check(_fn("sequence_ops", "ssb_dynamic_tanh")(
+        _ptr(x), _ptr(rows), _ptr(alpha), _ptr(weight), _ptr(bias), _ptr(out), c_int(dtype_code(out.dtype)), c_int(n),
+        c_int(width), c_int(1 if pdl else 0), _stream()), "dynamic_tanh")
+
+
+def shift_mix(h: torch.Tensor, mu: torch.Tensor, last: torch.Tensor, cu_new: torch.Tensor, seq_slot: torch.Tensor,
+              out: torch.Tensor, max_new: int, pdl: bool = False) -> None:
+    """out[s, t] = h[t] + (h[t-1] - h[t]) * mu[s] for every mix s; the row before a step's first token is
+    ``last[slot]`` (float32; zeros at a sequence's start), which afterwards holds the step's last h."""
+    _need(h, "h", None, 2); _need(mu, "mu", torch.float32, 2); _need(last, "last", torch.float32, 2)
+    _need(out, "out", h.dtype, 3)
+    T, W = h.shape
+    if tuple(out.shape) != (mu.shape[0], T, W) or mu.shape[1] != W or last.shape[1] != W or not mu.is_contiguous() \
+            or not last.is_contiguous() or cu_new.shape[0] != seq_slot.shape[0] + 1:
+        raise KernelError("shift_mix: shapes")
+    _check(_fn("sequence_ops", "ssb_shift_mix")(
+        _ptr(h), c_int(h.stride(0)), c_int(dtype_code(h.dtype)), _ptr(mu), c_int(mu.shape[0]), _ptr(last), _ptr(cu_new),
+        _ptr(seq_slot), _ptr(out), c_longlong(T * W), c_int(W), c_int(seq_slot.shape[0]), c_int(max_new), c_int(W),
+        c_int(1 if pdl else 0), _stream()), "shift_mix")
+
+
+CONV_MAX_TAPS = 16
+
+
+def causal_conv(x: torch.Tensor, x_bias: Optional[torch.Tensor], weight: torch.Tensor, bias: Optional[torch.Tensor],
+                tail: torch.Tensor, cu_new: torch.Tensor, seq_slot: torch.Tensor, out: torch.Tensor, max_new: int,
+                pdl: bool = False) -> None:
+    """out[t, c] = bias[c] + sum_j weight[c, j] * in[t - (taps - 1 - j), c] with in = x + x_bias; inputs from before
+    the step are ``tail[slot]`` ([taps - 1, channels] float32, oldest first), which is brought up to date."""
+    _need(x, "x", None, 2); _need(weight, "weight", torch.float32, 2); _need(tail, "tail", torch.float32, 2)
+    _need(out, "out", x.dtype, 2)
+    C, taps = weight.shape
+    if taps > CONV_MAX_TAPS or x.shape[1] < C or out.shape[1] < C or out.shape[0] != x.shape[0] \
+            or tail.shape[1] != max(taps - 1, 1) * C and tail.shape[1] != (taps - 1) * C or not weight.is_contiguous() \
+            or not tail.is_contiguous() or cu_new.shape[0] != seq_slot.shape[0] + 1:
+        raise KernelError(f"causal_conv: shapes (up to {CONV_MAX_TAPS} taps)")
+    for v in (x_bias, bias):
+        if v is not None:
+            _need(v, "bias", torch.float32, 1)
+            if v.shape[0] != C:
+                raise KernelError("causal_conv: one bias per channel")
+    _check(_fn("sequence_ops", "ssb_causal_conv")(
+        _ptr(x), c_int(x.stride(0)), c_int(dtype_code(x.dtype)), _ptr(x_bias), _ptr(weight), _ptr(bias), _ptr(tail),
+        _ptr(cu_new), _ptr(seq_slot), _ptr(out), c_int(out.stride(0)), c_int(seq_slot.shape[0]), c_int(max_new),
+        c_int(C), c_int(taps), c_int(1 if pdl else 0), _stream()), "causal_conv")
+
+
+def concat_cast(x: torch.Tensor, x0: torch.Tensor, act: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+                pdl: bool = False) -> None:
+    """act[t] = [x[t] | x0[t]] in ``act``'s type; out[t] = bias (zeros without one)."""
+    _need(x, "x", torch.float32, 2); _need(x0, "x0", torch.float32, 2); _need(act, "act", None, 2)
+    _need(out, "out", torch.float32, 2)
+    T, W = x.shape
+    if tuple(x0.shape) != (T, W) or tuple(act.shape) != (T, 2 * W) or tuple(out.shape) != (T, W) \
+            or not (x.is_contiguous() and x0.is_contiguous() and act.is_contiguous() and out.is_contiguous()):
+        raise KernelError("concat_cast: shapes")
+    if bias is not None:
+        _need(bias, "bias", torch.float32, 1)
+        if bias.shape[0] != W:
+            raise KernelError("concat_cast: bias")
+    _check(_fn("sequence_ops", "ssb_concat_cast")(
+        _ptr(x), _ptr(x0), _ptr(act), c_int(dtype_code(act.dtype)), _ptr(bias), _ptr(out), c_int(T), c_int(W),
+        c_int(1 if pdl else 0), _stream()), "concat_cast")
+
+
+def rms_pair_add(residual: torch.Tensor, a: torch.Tensor, wa: torch.Tensor, b: torch.Tensor, wb: torch.Tensor,
+                 eps: float, scale: float, pdl: bool = False) -> None:
+    """residual[t] += scale * (a[t] / rms(a[t]) * wa + b[t] / rms(b[t]) * wb), all float32."""
+    for name, v in (("residual", residual), ("a", a), ("b", b)):
+        _need(v, name, torch.float32, 2)
+        if v.shape != residual.shape or not v.is_contiguous():
+            raise KernelError("rms_pair_add: shapes")
+    _need(wa, "wa", torch.float32, 1); _need(wb, "wb", torch.float32, 1)
+    if wa.shape[0] != residual.shape[1] or wb.shape[0] != residual.shape[1]:
+        raise KernelError("rms_pair_add: weights")
+    _check(_fn("sequence_ops", "ssb_rms_pair_add")(
+        _ptr(residual), _ptr(a), _ptr(wa), _ptr(b), _ptr(wb), c_float(eps), c_float(scale), c_int(residual.shape[0]),
+        c_int(residual.shape[1]), c_int(1 if pdl else 0), _stream()), "rms_pair_add")
+
+
+def tanh_(x: torch.Tensor, pdl: bool = False) -> None:
+    """x <- tanh(x) in place; ``x`` [rows, n] may be a view into wider rows."""
+    _need(x, "x", None, 2)
+    _check(_fn("sequence_ops", "ssb_tanh")(_ptr(x), c_int(x.stride(0)), c_int(dtype_code(x.dtype)), c_int(x.shape[0]),
+                                           c_int(x.shape[1]), c_int(1 if pdl else 0), _stream()), "tanh")
+
+
+# ---- attention with sigmoid weights ----------------------------------------------------------
+def qk_norm_rope_append(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor],
+                        eps: float, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], pos: torch.Tensor,
+                        slot: torch.Tensor, page_table: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                        n_q: int, n_kv: int, dim: int, vdim: int, rot_dims: int, page_shift: int,
+                        write_cache: bool = True, pdl: bool = False) -> None:
+    """Rows [q (n_q x dim) | k (n_kv x dim) | v (n_kv x vdim)]: every q and k head is divided by its root mean
+    square (eps inside the root) and multiplied by the weight vector of its kind, its first ``rot_dims``
+    coordinates are rotated by the token's position (i with i + rot_dims/2); q is written back in place, k and
+    v go to the token's place in the paged cache."""
+    _need(qkv, "qkv", None, 2); _need(pos, "pos", torch.int32, 1); _need(slot, "slot", torch.int32, 1)
+    _need(page_table, "page_table", torch.int32, 2)
+    T = qkv.shape[0]
+    if qkv.shape[1] < n_q * dim + (n_kv * (dim + vdim) if write_cache else 0) or pos.shape[0] != T or slot.shape[0] != T:
+        raise KernelError("qk_norm_rope_append: rows are too narrow, or not one position and slot per token")
+    for w in (q_weight, k_weight):
+        if w is not None:
+            _need(w, "norm weight", torch.float32, 1)
+            if w.shape[0] != dim:
+                raise KernelError("qk_norm_rope_append: a norm weight per coordinate of a head")
+    positions = 0
+    if cos is not None and rot_dims:
+        _need(cos, "cos", torch.float32, 2); _need(sin, "sin", torch.float32, 2)
+        if cos.shape != sin.shape or cos.shape[1] * 2 != rot_dims or not (cos.is_contiguous() and sin.is_contiguous()):
+            raise KernelError("qk_norm_rope_append: cos/sin must be [positions, rot_dims/2], contiguous")
+        positions = cos.shape[0]
+    else:
+        cos = sin = None
+    if write_cache:
+        _need(k_cache, "k_cache", qkv.dtype); _need(v_cache, "v_cache", qkv.dtype)
+        if not (k_cache.is_contiguous() and v_cache.is_contiguous()) or k_cache.shape[-1] != dim or v_cache.shape[-1] != vdim:
+            raise KernelError("qk_norm_rope_append: cache rows of dim and vdim, contiguous")
+    _check(_fn("gated_attention", "ssb_qk_norm_rope_append")(
+        _ptr(qkv), c_int(qkv.stride(0)), c_int(dtype_code(qkv.dtype)), _ptr(q_weight), _ptr(k_weight), c_float(eps),
+        _ptr(cos), _ptr(sin), c_int(positions), _ptr(pos), _ptr(slot), _ptr(page_table), c_int(page_table.shape[1]),
+        _ptr(k_cache), _ptr(v_cache), c_int(T), c_int(n_q), c_int(n_kv), c_int(dim), c_int(vdim), c_int(rot_dims),
+        c_int(page_shift), c_int(1 if write_cache else 0), c_int(1 if pdl else 0), _stream()), "qk_norm_rope_append")
+
+
+def sigmoid_attention_plain(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, pos: torch.Tensor,
+                            slot: torch.Tensor, page_table: torch.Tensor, bias: Optional[torch.Tensor],
+                            out: torch.Tensor, n_q: int, n_kv: int, dim: int, vdim: int, page_shift: int,
+                            chunk: Optional[int], window: Optional[int], scale: float, pdl: bool = False) -> None:
+    """out[t, h] = sum_j sigmoid((q . k_j) * scale + bias[h]) v_j over the keys j <= pos of the token's slot that lie
+    in the same chunk of ``chunk`` positions (counted from position 0) and within ``window``."""
+    _need(q, "q", None, 2); _need(out, "out", q.dtype, 2); _need(k_cache, "k_cache", q.dtype); _need(v_cache, "v_cache", q.dtype)
+    _need(pos, "pos", torch.int32, 1); _need(slot, "slot", torch.int32, 1); _need(page_table, "page_table", torch.int32, 2)
+    T = q.shape[0]
+    if out.shape[0] != T or out.shape[1] < n_q * vdim or q.shape[1] < n_q * dim or n_q % n_kv:
+        raise KernelError("sigmoid_attention: q/out shapes")
+    if bias is not None:
+        _need(bias, "bias", torch.float32, 1)
+        if bias.shape[0] != n_q:
+            raise KernelError("sigmoid_attention: one bias per query head")
+    _check(_fn("gated_attention", "ssb_sigmoid_attention_plain")(
+        _ptr(q), c_int(q.stride(0)), c_int(dtype_code(q.dtype)), _ptr(k_cache), _ptr(v_cache), _ptr(pos), _ptr(slot),
+        _ptr(page_table), c_int(page_table.shape[1]), _ptr(bias), _ptr(out), c_int(out.stride(0)), c_int(T), c_int(n_q),
+        c_int(n_kv), c_int(dim), c_int(vdim), c_int(page_shift), c_int(int(chunk) if chunk else 0),
+        c_int(int(window) if window else 0), c_float(scale), c_int(1 if pdl else 0), _stream()), "sigmoid_attention_plain")
 
 
 # ---- experts -----------------------------------------------------------------------------

@@ -261,13 +261,15 @@ SSB_API int ssb_gated_linear_scan(const void* proj, int ld, int dtype, int q_off
 }
 
 // ---------------------------------------------------------------------------------------
-// y[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * w * silu(gate[t, h, :]): a head's
-// output normalised over its own width with one weight vector for all heads, then gated
+// y[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * w * act(gate[t, h, :]): a head's
+// output normalised over its own width, weighted (one weight vector for all heads, or w_stride = vdim:
+// one per head), then gated; act is silu (gate_kind 0), sigmoid (1), or the gate as it is (2: the
+// caller has applied its activation already)
 // ---------------------------------------------------------------------------------------
 template <typename T, typename TW>
 __global__ void __launch_bounds__(128)
-head_norm_gate_kernel(const float* __restrict__ o, int ldo, const TW* __restrict__ w, float eps,
-                      const T* __restrict__ gate, int ldg, T* __restrict__ y, int ldy, int vdim) {
+head_norm_gate_kernel(const float* __restrict__ o, int ldo, const TW* __restrict__ w, int w_stride, float eps,
+                      const T* __restrict__ gate, int ldg, int gate_kind, T* __restrict__ y, int ldy, int vdim) {
     __shared__ float red[128];
     const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
     ssb_pdl_launch_dependents();
@@ -283,27 +285,350 @@ head_norm_gate_kernel(const float* __restrict__ o, int ldo, const TW* __restrict
     }
     const float inv = 1.0f / sqrtf(red[0] / (float)vdim + eps);
     const T* gr = gate + (size_t)t * ldg + (size_t)h * vdim;
+    const TW* wr = w + (size_t)h * w_stride;
     T* dst = y + (size_t)t * ldy + (size_t)h * vdim;
     for (int c = tid; c < vdim; c += 128) {
         const float gv = ssb_to_float(gr[c]);
-        dst[c] = ssb_from_float<T>(src[c] * inv * ssb_to_float(w[c]) * (gv / (1.0f + expf(-gv))));
+        const float sg = 1.0f / (1.0f + expf(-gv));
+        const float ga = gate_kind == 0 ? gv * sg : gate_kind == 1 ? sg : gv;
+        dst[c] = ssb_from_float<T>(src[c] * inv * ssb_to_float(wr[c]) * ga);
     }
 }
 
-SSB_API int ssb_head_norm_gate(const float* o, int ldo, const void* w, int w_dtype, float eps, const void* gate,
-                               int ldg, void* y, int ldy, int dtype, int n_tokens, int n_heads, int vdim, int pdl,
-                               cudaStream_t stream) {
+SSB_API int ssb_head_norm_gate(const float* o, int ldo, const void* w, int w_dtype, int w_stride, float eps,
+                               const void* gate, int ldg, int gate_kind, void* y, int ldy, int dtype, int n_tokens,
+                               int n_heads, int vdim, int pdl, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (vdim <= 0 || n_heads <= 0 || n_heads > 65535) return SSB_ERR_BAD_SIZE;
+    if (vdim <= 0 || n_heads <= 0 || n_heads > 65535 || gate_kind < 0 || gate_kind > 2) return SSB_ERR_BAD_SIZE;
     const dim3 grid(n_tokens, n_heads);
     int rc = 0;
 #define SSB_HNG(T, TW) \
-    rc = ssb_launch(head_norm_gate_kernel<T, TW>, grid, dim3(128), 0, stream, pdl != 0, o, ldo, (const TW*)w, eps, \
-                    (const T*)gate, ldg, (T*)y, ldy, vdim)
+    rc = ssb_launch(head_norm_gate_kernel<T, TW>, grid, dim3(128), 0, stream, pdl != 0, o, ldo, (const TW*)w, w_stride, eps, \
+                    (const T*)gate, ldg, gate_kind, (T*)y, ldy, vdim)
     if (dtype == SSB_F32 && w_dtype == SSB_F32) SSB_HNG(float, float);
     else if (dtype == SSB_BF16 && w_dtype == SSB_BF16) SSB_HNG(bf16, bf16);
     else if (dtype == SSB_BF16 && w_dtype == SSB_F32) SSB_HNG(bf16, float);
+    else if (dtype == SSB_F32 && w_dtype == SSB_BF16) SSB_HNG(float, bf16);
     else return SSB_ERR_BAD_DTYPE;
 #undef SSB_HNG
+    return rc ? rc : ssb_launch_status();
+}
+
+// =======================================================================================
+// Two more recurrences over a matrix state S [dim, vdim] per head, and one over a vector state.
+//
+// Delta rule with decay and removal (DELTA): with a unit key u and a removal rate a per key channel,
+//     S_t = diag(w_t) S_(t-1) - (a_t * u_t) (u_t^T S_(t-1)) + k_t v_t^T,    o_t = S_t^T r_t
+// (both the decayed and the removed part read the old state).
+// Decay with a bonus for the token at hand (!DELTA):
+//     o_t = (S_(t-1) + diag(b) k_t v_t^T)^T r_t,    S_t = diag(w_t) S_(t-1) + k_t v_t^T
+// What enters besides r, k and v (the decays w, u, a * u) is float32 and made by the prepare kernel below.
+// =======================================================================================
+constexpr int MS_LANES = 8;          // lanes that share a value column: each owns a run of its rows
+constexpr int MS_COLS = 16;          // value columns a block of 128 threads owns
+constexpr int MS_TOKENS = 4;         // tokens staged per pair of barriers
+constexpr int MS_THREADS = MS_LANES * MS_COLS;
+
+// Decays in place and, for the delta rule, unit keys and removal vectors.  One block per (token, head).
+//   decay_kind 0: z <- exp(-exp(z + z_bias));  1: z <- exp(-decay_scale * sigmoid(z + z_bias))
+//   with_unit: unit[t] = [u | a * u], u = k / sqrt(sum(k^2) + unit_eps), a = sigmoid(a_pre + a_bias)
+template <typename T>
+__global__ void __launch_bounds__(64)
+state_scan_prepare_kernel(float* __restrict__ z, int ldz, const float* __restrict__ z_bias, int decay_kind,
+                          float decay_scale, const T* __restrict__ proj, int ld, int k_off, int a_off,
+                          const float* __restrict__ a_bias, float unit_eps, float* __restrict__ unit, int ldu,
+                          int n_heads, int dim) {
+    __shared__ float red[64];
+    ssb_pdl_launch_dependents();
+    ssb_pdl_wait();
+    const size_t t = blockIdx.x;
+    const int h = blockIdx.y, tid = threadIdx.x;
+    float* zr = z + t * ldz + (size_t)h * dim;
+    for (int i = tid; i < dim; i += 64) {
+        const float v = zr[i] + z_bias[h * dim + i];
+        zr[i] = decay_kind == 0 ? expf(-expf(v)) : expf(-decay_scale / (1.0f + expf(-v)));
+    }
+    if (unit == nullptr) return;
+    const T* kr = proj + t * ld + k_off + (size_t)h * dim;
+    const T* ar = proj + t * ld + a_off + (size_t)h * dim;
+    float part = 0.f;
+    for (int i = tid; i < dim; i += 64) {
+        const float k = ssb_to_float(kr[i]);
+        part = fmaf(k, k, part);
+    }
+    red[tid] = part;
+    __syncthreads();
+    for (int s = 32; s > 0; s >>= 1) {
+        if (tid < s) red[tid] += red[tid + s];
+        __syncthreads();
+    }
+    const float inv = 1.0f / sqrtf(red[0] + unit_eps);
+    float* ur = unit + t * ldu + (size_t)h * dim;
+    float* aur = ur + (size_t)n_heads * dim;
+    for (int i = tid; i < dim; i += 64) {
+        const float u = ssb_to_float(kr[i]) * inv;
+        const float a = 1.0f / (1.0f + expf(-(ssb_to_float(ar[i]) + a_bias[h * dim + i])));
+        ur[i] = u;
+        aur[i] = a * u;
+    }
+}
+
+SSB_API int ssb_state_scan_prepare(float* z, int ldz, const float* z_bias, int decay_kind, float decay_scale,
+                                   const void* proj, int ld, int dtype, int k_off, int a_off, const float* a_bias,
+                                   float unit_eps, float* unit, int ldu, int n_tokens, int n_heads, int dim, int pdl,
+                                   cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (n_heads <= 0 || n_heads > 65535 || dim <= 0 || decay_kind < 0 || decay_kind > 1) return SSB_ERR_BAD_SIZE;
+    const dim3 grid(n_tokens, n_heads);
+    int rc;
+    if (dtype == SSB_F32)
+        rc = ssb_launch(state_scan_prepare_kernel<float>, grid, dim3(64), 0, stream, pdl != 0, z, ldz, z_bias, decay_kind,
+                        decay_scale, (const float*)proj, ld, k_off, a_off, a_bias, unit_eps, unit, ldu, n_heads, dim);
+    else if (dtype == SSB_BF16)
+        rc = ssb_launch(state_scan_prepare_kernel<bf16>, grid, dim3(64), 0, stream, pdl != 0, z, ldz, z_bias, decay_kind,
+                        decay_scale, (const bf16*)proj, ld, k_off, a_off, a_bias, unit_eps, unit, ldu, n_heads, dim);
+    else
+        return SSB_ERR_BAD_DTYPE;
+    return rc ? rc : ssb_launch_status();
+}
+
+// A block walks the new tokens of one sequence for one head and 16 value columns.  Eight lanes share a
+// column: lane s owns rows s * RPL .. s * RPL + RPL - 1 of it in registers, and the sums over rows that a
+// token needs (u^T S before the update, S^T r after it) are three shuffle steps.  The vectors of four
+// tokens are staged in shared memory per pair of barriers while the next four are on their way.
+template <typename T, int RPL, bool DELTA>
+__global__ void __launch_bounds__(MS_THREADS)
+matrix_state_scan_kernel(const T* __restrict__ proj, int ld, int r_off, int k_off, int v_off,
+                         const float* __restrict__ decay, int ldd, const float* __restrict__ unit, int ldu,
+                         const float* __restrict__ bonus, float* __restrict__ state, const int* __restrict__ cu_new,
+                         const int* __restrict__ seq_slot, float* __restrict__ out, int ldo, int n_heads, int dim,
+                         int vdim) {
+    constexpr int DIMP = MS_LANES * RPL;                 // padded rows
+    constexpr int NV = DELTA ? 5 : 3;                    // staged vectors per token: w, k, r (, u, a * u)
+    constexpr int ITEMS = (MS_TOKENS * NV * DIMP + MS_THREADS - 1) / MS_THREADS;
+    __shared__ __align__(16) float vec[NV][MS_TOKENS][DIMP];
+    __shared__ float v_s[MS_TOKENS][MS_COLS];
+    const int b = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * MS_COLS;
+    const int tid = threadIdx.x, sub = tid % MS_LANES, cj = tid / MS_LANES;
+    ssb_pdl_launch_dependents();
+    ssb_pdl_wait();
+    const int slot = seq_slot[b];
+    if (slot < 0) return;
+    const int t0 = cu_new[b], t1 = cu_new[b + 1];
+    if (t0 >= t1) return;
+    const bool col = j0 + cj < vdim;
+    float* S = state + ((size_t)slot * n_heads + h) * dim * vdim;
+    float s_reg[RPL], b_reg[RPL];
+#pragma unroll
+    for (int r = 0; r < RPL; ++r) {
+        const int i = sub * RPL + r;
+        s_reg[r] = (col && i < dim) ? S[(size_t)i * vdim + j0 + cj] : 0.f;
+        b_reg[r] = (!DELTA && bonus != nullptr && i < dim) ? bonus[h * dim + i] : 0.f;
+    }
+    for (int e = tid; e < NV * MS_TOKENS * DIMP; e += MS_THREADS) (&vec[0][0][0])[e] = 0.f;   // the padding stays zero
+    // item n * MS_THREADS + tid of a turn is (vector, token, channel); the same in every turn
+    float val[ITEMS], vv = 0.f;
+    int item_v[ITEMS], item_tt[ITEMS], item_i[ITEMS];
+#pragma unroll
+    for (int n = 0; n < ITEMS; ++n) {
+        const int item = n * MS_THREADS + tid;
+        const int per = MS_TOKENS * dim;
+        item_v[n] = item < NV * per ? item / per : NV;
+        item_tt[n] = (item % per) / dim;
+        item_i[n] = item % dim;
+    }
+    auto fetch = [&](int t) {
+        const int n_tok = min(MS_TOKENS, t1 - t);
+#pragma unroll
+        for (int n = 0; n < ITEMS; ++n) {
+            const int v = item_v[n], tt = item_tt[n], i = item_i[n];
+            if (v < NV && tt < n_tok) {
+                const size_t row = (size_t)(t + tt);
+                const int c = h * dim + i;
+                val[n] = v == 0 ? decay[row * ldd + c]
+                       : v == 1 ? ssb_to_float(proj[row * ld + k_off + c])
+                       : v == 2 ? ssb_to_float(proj[row * ld + r_off + c])
+                       : v == 3 ? unit[row * ldu + c]
+                                : unit[row * ldu + n_heads * dim + c];
+            }
+        }
+        if (tid < MS_TOKENS * MS_COLS) {
+            const int tt = tid / MS_COLS, jj = tid % MS_COLS;
+            vv = (tt < n_tok && j0 + jj < vdim) ? ssb_to_float(proj[(size_t)(t + tt) * ld + v_off + h * vdim + j0 + jj]) : 0.f;
+        }
+    };
+    fetch(t0);
+    __syncthreads();
+    for (int t = t0; t < t1; t += MS_TOKENS) {
+        const int n_tok = min(MS_TOKENS, t1 - t);
+#pragma unroll
+        for (int n = 0; n < ITEMS; ++n)
+            if (item_v[n] < NV && item_tt[n] < n_tok) vec[item_v[n]][item_tt[n]][item_i[n]] = val[n];
+        if (tid < MS_TOKENS * MS_COLS) v_s[tid / MS_COLS][tid % MS_COLS] = vv;
+        __syncthreads();
+        if (t + MS_TOKENS < t1) fetch(t + MS_TOKENS);
+        for (int tt = 0; tt < n_tok; ++tt) {
+            const float v = v_s[tt][cj];
+            const float4* w4 = reinterpret_cast<const float4*>(&vec[0][tt][sub * RPL]);
+            const float4* k4 = reinterpret_cast<const float4*>(&vec[1][tt][sub * RPL]);
+            const float4* r4 = reinterpret_cast<const float4*>(&vec[2][tt][sub * RPL]);
+            float o = 0.f;
+            if (DELTA) {
+                const float4* u4 = reinterpret_cast<const float4*>(&vec[NV - 2][tt][sub * RPL]);
+                const float4* au4 = reinterpret_cast<const float4*>(&vec[NV - 1][tt][sub * RPL]);
+                float seen = 0.f;
+#pragma unroll
+                for (int r = 0; r < RPL; r += 4) {
+                    const float4 u = u4[r >> 2];
+                    seen = fmaf(u.x, s_reg[r], seen);
+                    seen = fmaf(u.y, s_reg[r + 1], seen);
+                    seen = fmaf(u.z, s_reg[r + 2], seen);
+                    seen = fmaf(u.w, s_reg[r + 3], seen);
+                }
+                seen += __shfl_xor_sync(0xffffffffu, seen, 1);
+                seen += __shfl_xor_sync(0xffffffffu, seen, 2);
+                seen += __shfl_xor_sync(0xffffffffu, seen, 4);
+#pragma unroll
+                for (int r = 0; r < RPL; r += 4) {
+                    const float4 w = w4[r >> 2], k = k4[r >> 2], q = r4[r >> 2], au = au4[r >> 2];
+                    s_reg[r] = fmaf(w.x, s_reg[r], fmaf(k.x, v, -au.x * seen));          o = fmaf(s_reg[r], q.x, o);
+                    s_reg[r + 1] = fmaf(w.y, s_reg[r + 1], fmaf(k.y, v, -au.y * seen));  o = fmaf(s_reg[r + 1], q.y, o);
+                    s_reg[r + 2] = fmaf(w.z, s_reg[r + 2], fmaf(k.z, v, -au.z * seen));  o = fmaf(s_reg[r + 2], q.z, o);
+                    s_reg[r + 3] = fmaf(w.w, s_reg[r + 3], fmaf(k.w, v, -au.w * seen));  o = fmaf(s_reg[r + 3], q.w, o);
+                }
+            } else {
+#pragma unroll
+                for (int r = 0; r < RPL; r += 4) {
+                    const float4 w = w4[r >> 2], k = k4[r >> 2], q = r4[r >> 2];
+                    const float kv0 = k.x * v, kv1 = k.y * v, kv2 = k.z * v, kv3 = k.w * v;
+                    o = fmaf(fmaf(b_reg[r], kv0, s_reg[r]), q.x, o);          s_reg[r] = fmaf(w.x, s_reg[r], kv0);
+                    o = fmaf(fmaf(b_reg[r + 1], kv1, s_reg[r + 1]), q.y, o);  s_reg[r + 1] = fmaf(w.y, s_reg[r + 1], kv1);
+                    o = fmaf(fmaf(b_reg[r + 2], kv2, s_reg[r + 2]), q.z, o);  s_reg[r + 2] = fmaf(w.z, s_reg[r + 2], kv2);
+                    o = fmaf(fmaf(b_reg[r + 3], kv3, s_reg[r + 3]), q.w, o);  s_reg[r + 3] = fmaf(w.w, s_reg[r + 3], kv3);
+                }
+            }
+            o += __shfl_xor_sync(0xffffffffu, o, 1);
+            o += __shfl_xor_sync(0xffffffffu, o, 2);
+            o += __shfl_xor_sync(0xffffffffu, o, 4);
+            if (sub == 0 && col) out[(size_t)(t + tt) * ldo + h * vdim + j0 + cj] = o;
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int r = 0; r < RPL; ++r) {
+        const int i = sub * RPL + r;
+        if (col && i < dim) S[(size_t)i * vdim + j0 + cj] = s_reg[r];
+    }
+}
+
+// proj [T, ld]: r, k (n_heads x dim) and v (n_heads x vdim) from the given columns; decay [T, ldd] float32
+// (n_heads x dim); kind 0 (delta rule): unit [T, ldu] float32 = [u | a * u]; kind 1: bonus [n_heads x dim]
+// float32 or null; state [slots, n_heads, dim, vdim] float32; out [T, ldo] float32 (n_heads x vdim).
+SSB_API int ssb_matrix_state_scan(const void* proj, int ld, int dtype, int r_off, int k_off, int v_off,
+                                  const float* decay, int ldd, int kind, const float* unit, int ldu, const float* bonus,
+                                  float* state, const int* cu_new, const int* seq_slot, float* out, int ldo, int n_seqs,
+                                  int n_heads, int dim, int vdim, int pdl, cudaStream_t stream) {
+    if (n_seqs <= 0) return 0;
+    if (dim <= 0 || dim > 256 || vdim <= 0 || n_heads <= 0 || (kind != 0 && kind != 1)) return SSB_ERR_BAD_SIZE;
+    if (kind == 0 && unit == nullptr) return SSB_ERR_BAD_SIZE;
+    const dim3 grid(n_seqs, n_heads, (vdim + MS_COLS - 1) / MS_COLS);
+    if (grid.y > 65535 || grid.z > 65535) return SSB_ERR_BAD_SIZE;
+    int rc = 0;
+#define SSB_MS(T, RPL, DELTA) \
+    rc = ssb_launch(matrix_state_scan_kernel<T, RPL, DELTA>, grid, dim3(MS_THREADS), 0, stream, pdl != 0, (const T*)proj, ld, \
+                    r_off, k_off, v_off, decay, ldd, unit, ldu, bonus, state, cu_new, seq_slot, out, ldo, n_heads, dim, vdim)
+#define SSB_MS_DIM(T, DELTA) do { \
+        if (dim <= 32) SSB_MS(T, 4, DELTA); \
+        else if (dim <= 64) SSB_MS(T, 8, DELTA); \
+        else if (dim <= 128) SSB_MS(T, 16, DELTA); \
+        else SSB_MS(T, 32, DELTA); \
+    } while (0)
+    if (dtype == SSB_F32) { if (kind == 0) SSB_MS_DIM(float, true); else SSB_MS_DIM(float, false); }
+    else if (dtype == SSB_BF16) { if (kind == 0) SSB_MS_DIM(bf16, true); else SSB_MS_DIM(bf16, false); }
+    else return SSB_ERR_BAD_DTYPE;
+#undef SSB_MS_DIM
+#undef SSB_MS
+    return rc ? rc : ssb_launch_status();
+}
+
+// ---------------------------------------------------------------------------------------
+// The real-gated linear recurrent unit: a state value per channel,
+//     r = sigmoid(g_r + b_r), i = sigmoid(g_i + b_i), log a = rate * r (rate = -8 softplus(lambda) < 0),
+//     S_t = a S_(t-1) + sqrt(1 - a^2) * i * u_t,        out_t = S_t * gelu_tanh(y_t + y_bias)
+// gates [T, ldg] float32 holds, per block of `block` channels, [g_r (block) | g_i (block)].
+// One thread per (sequence, channel), four tokens fetched ahead.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+gated_unit_scan_kernel(const float* __restrict__ gates, int ldg, const float* __restrict__ bias_r,
+                       const float* __restrict__ bias_i, const float* __restrict__ rate, const T* __restrict__ u,
+                       int ldu, const T* __restrict__ y, int ldy, const float* __restrict__ y_bias,
+                       float* __restrict__ state, const int* __restrict__ cu_new, const int* __restrict__ seq_slot,
+                       T* __restrict__ out, int ldo, int channels, int block) {
+    constexpr int AHEAD = 4;
+    ssb_pdl_launch_dependents();
+    ssb_pdl_wait();
+    const int b = blockIdx.x, c = blockIdx.y * 128 + threadIdx.x;
+    const int slot = seq_slot[b];
+    if (slot < 0 || c >= channels) return;
+    const int t0 = cu_new[b], t1 = cu_new[b + 1];
+    const int gc = (c / block) * 2 * block + c % block;           // where the channel's g_r sits; g_i is `block` on
+    const float br = bias_r[c], bi = bias_i[c], rt = rate[c], yb = y_bias ? y_bias[c] : 0.f;
+    float S = state[(size_t)slot * channels + c];
+    float gr[AHEAD], gi[AHEAD], uu[AHEAD], yy[AHEAD];
+    auto fetch = [&](int t) {
+#pragma unroll
+        for (int n = 0; n < AHEAD; ++n)
+            if (t + n < t1) {
+                const size_t row = (size_t)(t + n);
+                gr[n] = gates[row * ldg + gc];
+                gi[n] = gates[row * ldg + gc + block];
+                uu[n] = ssb_to_float(u[row * ldu + c]);
+                yy[n] = ssb_to_float(y[row * ldy + c]);
+            }
+    };
+    fetch(t0);
+    for (int t = t0; t < t1; t += AHEAD) {
+        float cgr[AHEAD], cgi[AHEAD], cu[AHEAD], cy[AHEAD];
+#pragma unroll
+        for (int n = 0; n < AHEAD; ++n) { cgr[n] = gr[n]; cgi[n] = gi[n]; cu[n] = uu[n]; cy[n] = yy[n]; }
+        if (t + AHEAD < t1) fetch(t + AHEAD);
+#pragma unroll
+        for (int n = 0; n < AHEAD; ++n)
+            if (t + n < t1) {
+                const float r = 1.0f / (1.0f + expf(-(cgr[n] + br)));
+                const float i = 1.0f / (1.0f + expf(-(cgi[n] + bi)));
+                const float log_a = rt * r;
+                const float a = expf(log_a);
+                S = fmaf(a, S, sqrtf(-expm1f(2.0f * log_a)) * i * cu[n]);
+                out[(size_t)(t + n) * ldo + c] = ssb_from_float<T>(S * gelu_tanh_f(cy[n] + yb));
+            }
+    }
+    state[(size_t)slot * channels + c] = S;
+}
+
+SSB_API int ssb_gated_unit_scan(const float* gates, int ldg, const float* bias_r, const float* bias_i, const float* rate,
+                                const void* u, int ldu, const void* y, int ldy, const float* y_bias, float* state,
+                                const int* cu_new, const int* seq_slot, void* out, int ldo, int dtype, int n_seqs,
+                                int channels, int block, int pdl, cudaStream_t stream) {
+    if (n_seqs <= 0) return 0;
+    if (channels <= 0 || block <= 0 || channels % block) return SSB_ERR_BAD_SIZE;
+    const dim3 grid(n_seqs, (channels + 127) / 128);
+    if (grid.y > 65535) return SSB_ERR_BAD_SIZE;
+    int rc;
+    if (dtype == SSB_F32)
+        rc = ssb_launch(gated_unit_scan_kernel<float>, grid, dim3(128), 0, stream, pdl != 0, gates, ldg, bias_r, bias_i, rate,
+                        (const float*)u, ldu, (const float*)y, ldy, y_bias, state, cu_new, seq_slot, (float*)out, ldo,
+                        channels, block);
+    else if (dtype == SSB_BF16)
+        rc = ssb_launch(gated_unit_scan_kernel<bf16>, grid, dim3(128), 0, stream, pdl != 0, gates, ldg, bias_r, bias_i, rate,
+                        (const bf16*)u, ldu, (const bf16*)y, ldy, y_bias, state, cu_new, seq_slot, (bf16*)out, ldo,
+                        channels, block);
+    else
+        return SSB_ERR_BAD_DTYPE;
     return rc ? rc : ssb_launch_status();
 }

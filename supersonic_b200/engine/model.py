@@ -23,7 +23,7 @@ import torch
 from ..cache import SequenceCache
 from ..config import ModelSpec, load_config, spec_from_config
 from ..csrc.kernel_sets import kernel_set_for
-from ..parts import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS,
+from ..parts import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS, STREAM_ADAPTERS,
                      BuildContext, WeightAccess, lookup)
 from ..weights import WeightStore
 from .batch import (NotOnHost, PackedStep, StepBatch, StepEntry, batch_over, decode_pages_bucket, pack_entries,
@@ -61,6 +61,7 @@ class StepContext:
     stage: str = ""            # the part that is running ("embed", "mixer", "feed_forward", "head"): for stage timings
     streams: Any = None        # what a block arrangement keeps from layer to layer within one step (the stack of
                                # earlier layers' results for a weighted sum over depth)
+    embedded: Any = None       # the embedding's output of the step, for stream adapters that read it again
 
 
 class DecodeGraph:
@@ -223,12 +224,20 @@ class Model:
             self.blocks.append(lookup(BLOCKS, b.kind, "block")(mixer, ff, n1, n2, pos, **own))
         self.final_norm = part(NORMS, "norm", spec.final_norm)
         self.head = part(HEADS, "head", spec.head)
+        self.adapters = [part(STREAM_ADAPTERS, "stream adapter", a) for a in spec.adapters]
         weights.forget()
+        # an adapter that reads the embedding's output needs it kept apart if blocks run (and add into it) first
+        self._keep_embedding = any(getattr(a, "needs_embedding", False) for a in self.adapters) \
+            and spec.schedule[0].before is None
 
-        # what each cache entry must hold is asked of the mixer that writes it
-        needs: Dict[int, Any] = {}
+        # what each cache entry must hold is asked of the block that writes it (an arrangement without state
+        # of its own passes its mixer's answer on)
+        needs: Dict[Any, Any] = {}
+        if getattr(self.embedding, "cache_need", None) is not None:
+            needs[self.embedding.cache_key] = self.embedding.cache_need()
         for stop in spec.schedule:
-            need = self.blocks[stop.layer].mixer.cache_need()
+            block = self.blocks[stop.layer]
+            need = block.cache_need() if hasattr(block, "cache_need") else block.mixer.cache_need()
             if stop.writes_cache:
                 if stop.cache in needs and needs[stop.cache] != need:
                     raise ValueError(f"cache entry {stop.cache} is written by mixers with different needs")
@@ -245,7 +254,7 @@ class Model:
         # decode steps of the serving path replay captured graphs (one per batch size and page bucket),
         # if the kernel set can be captured and no part says that it cannot (``capture_safe = False``:
         # it reads host lists of the batch, or synchronises)
-        parts = [self.embedding, self.final_norm, self.head]
+        parts = [self.embedding, self.final_norm, self.head] + self.adapters
         for b in self.blocks:
             parts += [b] + [p for p in (getattr(b, n, None) for n in ("mixer", "feed_forward", "mixer_norm",
                                                                      "feed_forward_norm", "position")) if p is not None]
@@ -265,6 +274,8 @@ class Model:
         limits = [getattr(getattr(b, "position", None), "max_positions", None) for b in self.blocks]
         self.position_limit = min([int(x) for x in limits if x is not None], default=None)
         self._timed = None      # a TimedKernels while stage timing is on
+        self.layer_probe = None # callable(stop, stream) run after every stop of an uncaptured step (tests, debugging)
+        self._ones = None
         # NVTX ranges per layer (SSB200_NVTX=1): for a profiler's timeline of uncaptured steps; the reference
         # marks stages with host timers only (crates/runner/src/decode_engine.rs:10157-10162)
         self.nvtx = os.environ.get("SSB200_NVTX", "") not in ("", "0")
@@ -439,40 +450,65 @@ class Model:
             self._timed.ctx = ctx
         ctx.stage = "embed"
         residual = self.embedding(ctx, batch.token_ids)
+        if self.adapters:
+            ctx.embedded = residual
+            if self._keep_embedding:                        # blocks add into the stream in place: a copy stays as it was
+                ctx.embedded = torch.empty_like(residual)
+                ctx.kernels.stream_mix(residual.unsqueeze(0), self._one(), 1, ctx.embedded)
         if self.nvtx:                                       # a named range per stop of the schedule, for timelines
             for i, stop in enumerate(self.spec.schedule):
                 torch.cuda.nvtx.range_push(f"stop {i} layer {stop.layer}")
+                if stop.before is not None:
+                    residual = self.adapters[stop.before[0]](ctx, residual, stop.before[1])
                 moved = self.blocks[stop.layer].forward(ctx, residual, stop.cache, stop.writes_cache)
                 residual = residual if moved is None else moved
                 torch.cuda.nvtx.range_pop()
         else:
             # a block updates the stream in place, or returns the tensor that holds it from now on
             for stop in self.spec.schedule:
+                if stop.before is not None:
+                    residual = self.adapters[stop.before[0]](ctx, residual, stop.before[1])
                 moved = self.blocks[stop.layer].forward(ctx, residual, stop.cache, stop.writes_cache)
                 if moved is not None:
                     residual = moved
+                if self.layer_probe is not None:            # a debugging hook: the stream after every stop
+                    self.layer_probe(stop, residual)
         if batch.n_want == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
         ctx.stage = "head"
         normed = self.final_norm(ctx, residual, rows=batch.want_rows)
         return self.head(ctx, normed)
 
+    def _one(self) -> torch.Tensor:
+        if self._ones is None:
+            self._ones = torch.ones(1, dtype=torch.float32, device=self.device)
+        return self._ones
+
     # ---- what a step must read (for rooflines) ------------------------------------------------
     def weight_tensors(self) -> list:
         """Every device tensor the parts that run in a step hold (mixers, feed-forwards, norms, head),
         each storage once: a tied head and a fused view count with the tensor they share.  Position
         tables and the embedding table are left out: a step reads a row of them per token."""
-        parts = [self.final_norm, self.head]
-        for b in self.blocks:
-            parts += [getattr(b, n, None) for n in ("mixer", "feed_forward", "mixer_norm", "feed_forward_norm")]
+        parts = [self.final_norm, self.head] + list(self.adapters) + list(self.blocks)
         seen, out = set(), []
-        for p in parts:
-            for v in (vars(p).values() if p is not None and hasattr(p, "__dict__") else ()):
-                if isinstance(v, torch.Tensor) and v.device.type == "cuda" and v.dim() >= 1:
+
+        def take(v, depth=0):
+            if isinstance(v, torch.Tensor):
+                if v.device.type == "cuda" and v.dim() >= 1:
                     key = v.untyped_storage().data_ptr()
                     if key not in seen:
                         seen.add(key)
                         out.append(v)
+            elif isinstance(v, (list, tuple)):
+                for e in v:
+                    take(e, depth)
+            elif hasattr(v, "__dict__") and not isinstance(v, type) and \
+                    (depth < 2 or (depth < 4 and type(v).__module__.startswith("supersonic_b200.parts"))):
+                for name, e in vars(v).items():              # a part, and the parts it holds (a block's, a pair's halves)
+                    if name != "position":
+                        take(e, depth + 1)
+        for p in parts:
+            take(p)
         return out
 
     def weight_bytes(self) -> int:

@@ -24,7 +24,7 @@ from typing import Dict, Optional
 import torch
 
 from ..cache import SequenceCache
-from ..parts import FEED_FORWARDS, MIXERS, lookup
+from ..parts import BLOCKS, EMBEDDINGS, FEED_FORWARDS, MIXERS, STREAM_ADAPTERS, lookup
 
 GIB = float(1 << 30)
 
@@ -61,6 +61,7 @@ def _part_specs(spec):
                 yield p
     yield spec.final_norm
     yield spec.head
+    yield from spec.adapters
 
 
 def weight_bytes(spec, store, dtype: torch.dtype) -> int:
@@ -82,17 +83,23 @@ def weight_bytes(spec, store, dtype: torch.dtype) -> int:
     return total
 
 
-def cache_needs(spec) -> Dict[int, object]:
-    needs: Dict[int, object] = {}
+def cache_needs(spec) -> Dict[object, object]:
+    needs: Dict[object, object] = {}
+    emb = lookup(EMBEDDINGS, spec.embedding.kind, "embedding")
+    if getattr(emb, "cache_need_from", None) is not None:
+        needs[emb.cache_key] = emb.cache_need_from(spec.embedding.params)
     for stop in spec.schedule:
         if not stop.writes_cache:
             continue
-        ps = spec.blocks[stop.layer].mixer
+        b = spec.blocks[stop.layer]
+        ps = b.mixer
         hook = getattr(lookup(MIXERS, ps.kind, "mixer"), "cache_need_from", None)
-        if hook is not None:
-            need = hook(ps.params)
-            if need is not None:
-                needs[stop.cache] = need
+        need = hook(ps.params) if hook is not None else None
+        block_hook = getattr(lookup(BLOCKS, b.kind, "block"), "cache_need_from", None)
+        if block_hook is not None:                           # an arrangement that keeps state beside its mixer's
+            need = block_hook(b.params, need)
+        if need is not None:
+            needs[stop.cache] = need
     return needs
 
 
@@ -107,6 +114,9 @@ def workspace_bytes(spec, dtype: torch.dtype, step_tokens: int, decode_rows: int
             hook = getattr(lookup(table, ps.kind, what), "activation_elements", None)
             here = max(here, int(hook(ps.params)) if hook is not None else 4 * spec.hidden_size)
         widest = max(widest, here)
+    for a in spec.adapters:
+        hook = getattr(lookup(STREAM_ADAPTERS, a.kind, "stream adapter"), "activation_elements", None)
+        widest = max(widest, int(hook(a.params)) if hook is not None else 4 * spec.hidden_size)
     # an arrangement that keeps every layer's result within a step says how many float32 streams it holds
     streams = max([int(b.params.get("depth_average", {}).get("layers", 0)) + 2 if b.params.get("depth_average") else 1
                    for b in spec.blocks] + [1])

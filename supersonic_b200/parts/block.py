@@ -1,11 +1,13 @@
 """Block arrangements.  ``pre_norm``: h += mixer(norm(h)); h += feed_forward(norm(h)),
 the residual stream kept and summed in float32 (crates/runner/src/prefill_engine.rs:1116-1222).
-``parallel``: h += mixer(n) + feed_forward(n) with the one n = norm(h), optionally followed by a
-learned weighted sum over the results of all layers so far."""
+``parallel``: h += mixer(n) + feed_forward(n) with the one n = norm(h), or with a norm each (both of the
+same h); optionally the mixer's input is mixed with the previous token's (token shift), and optionally the
+layer is followed by a learned weighted sum over the results of all layers so far."""
 from __future__ import annotations
 
 import torch
 
+from ..cache import StateNeed
 from ..csrc.kernel_sets import NormedInput
 from .registry import register_block
 
@@ -40,7 +42,14 @@ class PreNormBlock:
 @register_block("parallel")
 class ParallelBlock:
     """x <- x + mixer(n) + feed_forward(n), n = norm(x): one norm, read by both sublayers (the
-    feed-forward may be absent).
+    feed-forward may be absent).  With a second norm: x <- x + mixer(norm_1(x)) + feed_forward(norm_2(x)), both
+    norms taken of the x that enters the layer.
+
+    ``params["token_shift"] = {"size": width}`` with the tensor ``shift`` [width]: the mixer reads
+    n_t + (n_(t-1) - n_t) * shift instead of n_t, where n_(t-1) is the previous token's normed row as it was
+    before this replacement (zeros for a sequence's first token).  The last row of a step is kept per
+    sequence: the block then asks the cache for ``{"mixer": the mixer's need, "shift": a row of width
+    floats}``, and the mixer gets the cache id ``(cache_id, "mixer")``.
 
     ``params["depth_average"] = {"index": i, "layers": L}`` adds a weighted sum over depth.  Call R_0 what the
     embedding gives and R_(n+1) = s_n + mixer(norm(s_n)) + feed_forward(norm(s_n)) the raw result of layer n,
@@ -52,9 +61,15 @@ class ParallelBlock:
 
     def __init__(self, mixer, feed_forward, mixer_norm, feed_forward_norm, position, params=None,
                  weights=None, build=None):
-        if feed_forward_norm is not None:
-            raise ValueError("a parallel block has one norm")
         self.mixer, self.feed_forward, self.mixer_norm, self.position = mixer, feed_forward, mixer_norm, position
+        self.feed_forward_norm = feed_forward_norm
+        self.shift = (params or {}).get("token_shift")
+        if self.shift is not None:
+            self.shift_size = int(self.shift["size"])
+            mu = build.weights.stored(weights["shift"]).float().reshape(1, -1).contiguous()
+            if tuple(mu.shape) != (1, self.shift_size):
+                raise ValueError(f"{weights['shift']} has shape {tuple(mu.shape[1:])}, expected ({self.shift_size},)")
+            self.shift_mu = mu
         self.depth = (params or {}).get("depth_average")
         if self.depth is not None:
             self.index, self.layers = int(self.depth["index"]), int(self.depth["layers"])
@@ -65,6 +80,19 @@ class ParallelBlock:
             self.one = torch.ones(1, dtype=torch.float32, device=build.device)
 
     _give = staticmethod(PreNormBlock._give)
+
+    def cache_need(self):
+        """What the block's stop of the schedule keeps per sequence: the mixer's need, and with token shift a
+        row of its own beside it."""
+        need = self.mixer.cache_need()
+        if self.shift is None:
+            return need
+        return {"mixer": need, "shift": StateNeed(self.shift_size)}
+
+    @staticmethod
+    def cache_need_from(params, mixer_need):
+        shift = (params or {}).get("token_shift")
+        return mixer_need if shift is None else {"mixer": mixer_need, "shift": StateNeed(int(shift["size"]))}
 
     def forward(self, ctx, residual, cache_id, writes_cache):
         if self.depth is not None:
@@ -77,11 +105,24 @@ class ParallelBlock:
                 raise RuntimeError("a depth-averaging layer ran before the first one of its step")
             residual = ctx.streams[self.index + 1]
         x = NormedInput(ctx, residual, self.mixer_norm)
+        x2 = x
+        if self.feed_forward is not None and self.feed_forward_norm is not None:
+            # the second norm reads the stream as it enters the layer: taken before the mixer adds to it
+            x2 = NormedInput(ctx, residual, self.feed_forward_norm)
+            x2.tensor()
         ctx.stage = "mixer"
-        self.mixer.forward(ctx, self._give(x, self.mixer), residual, cache_id, writes_cache, self.position)
+        if self.shift is not None:
+            if not writes_cache:
+                raise ValueError("a block with token shift keeps state: its stop must write its cache entry")
+            n = x.tensor()
+            mixed = torch.empty((1,) + tuple(n.shape), dtype=n.dtype, device=n.device)
+            ctx.kernels.shift_mix(n, self.shift_mu, ctx.cache.state((cache_id, "shift")), ctx.batch, mixed)
+            self.mixer.forward(ctx, mixed[0], residual, (cache_id, "mixer"), writes_cache, self.position)
+        else:
+            self.mixer.forward(ctx, self._give(x, self.mixer), residual, cache_id, writes_cache, self.position)
         if self.feed_forward is not None:
             ctx.stage = "feed_forward"
-            self.feed_forward.forward(ctx, self._give(x, self.feed_forward), residual)
+            self.feed_forward.forward(ctx, self._give(x2, self.feed_forward), residual)
         if self.depth is None:
             return None
         out = ctx.streams[self.index + 2]

@@ -1,6 +1,7 @@
 """Norms.  ``rmsnorm``: y = x * rsqrt(mean(x^2) + eps) * w, statistics in float32,
 one rounding at the end (kernels/full_attention_cuda.cuh:2826-2873; the weight is
-used as ``w``, not ``1 + w``: crates/runner/src/llama31_engine.rs:89)."""
+used as ``w``, not ``1 + w``: crates/runner/src/llama31_engine.rs:89).  ``dynamic_tanh``:
+y = tanh(alpha * x) * w + b, which takes no statistics of x at all."""
 from __future__ import annotations
 
 import torch
@@ -52,3 +53,31 @@ class ScalarRMSNorm(RMSNorm):
         g = g.reshape(1).expand(self.size).contiguous()
         self.weight = g.float() if build.dtype == torch.float32 else g
         self.dtype = build.dtype
+
+
+@register_norm("dynamic_tanh")
+class DynamicTanh:
+    """y = tanh(alpha * x) * w + b, element by element: no mean, no variance, no eps.
+
+    params: ``size``; weights: ``weight`` [size], ``bias`` [size], ``alpha`` (a single number).  The three are
+    kept in float32 (they are read once per element); the result has the activation type.
+    """
+
+    fusable_rms = False    # not a root-mean-square norm: kernels that fold one into a product must not take it
+
+    def __init__(self, params, weights, build: BuildContext):
+        self.size = int(params["size"])
+        w = build.weights
+        self.weight = w.stored(weights["weight"]).float().contiguous()
+        self.bias = w.stored(weights["bias"]).float().contiguous()
+        self.alpha = w.stored(weights["alpha"]).float().reshape(-1).contiguous()
+        if tuple(self.weight.shape) != (self.size,) or tuple(self.bias.shape) != (self.size,) or self.alpha.numel() != 1:
+            raise ValueError(f"{weights['weight']}: weight and bias of ({self.size},) and a single alpha expected, got "
+                             f"{tuple(self.weight.shape)}, {tuple(self.bias.shape)}, {tuple(self.alpha.shape)}")
+        self.dtype = build.dtype
+
+    def __call__(self, ctx, x, rows=None):
+        n = x.shape[0] if rows is None else rows.shape[0]
+        out = torch.empty((n, self.size), dtype=self.dtype, device=x.device)
+        ctx.kernels.dynamic_tanh(x, self.alpha, self.weight, self.bias, out, rows)
+        return out

@@ -23,6 +23,7 @@ POSITION_ENCODINGS: Dict[str, type] = {}
 BLOCKS: Dict[str, type] = {}
 EMBEDDINGS: Dict[str, type] = {}
 HEADS: Dict[str, type] = {}
+STREAM_ADAPTERS: Dict[str, type] = {}
 
 
 def _register(table: Dict[str, type], what: str) -> Callable[[str], Callable[[type], type]]:
@@ -41,6 +42,7 @@ register_position_encoding = _register(POSITION_ENCODINGS, "position encoding")
 register_block = _register(BLOCKS, "block")
 register_embedding = _register(EMBEDDINGS, "embedding")
 register_head = _register(HEADS, "head")
+register_stream_adapter = _register(STREAM_ADAPTERS, "stream adapter")
 
 
 def lookup(table: Dict[str, type], kind: str, what: str) -> type:

@@ -20,6 +20,8 @@ def scaled_inverse_frequencies(rotary_dim: int, theta: float, scaling: Optional[
     inv = 1.0 / (float(theta) ** (2.0 * i / rotary_dim))
     if not scaling:
         return inv
+    if scaling.get("kind") == "yarn":
+        return yarn_inverse_frequencies(rotary_dim, float(theta), scaling, inv)
     factor = float(scaling["factor"])
     low, high = float(scaling["low_freq_factor"]), float(scaling["high_freq_factor"])
     old = float(scaling["original_max_position_embeddings"])
@@ -30,9 +32,36 @@ def scaled_inverse_frequencies(rotary_dim: int, theta: float, scaling: Optional[
                        torch.where(wavelen < old / high, inv, blended))
 
 
+def yarn_inverse_frequencies(rotary_dim: int, theta: float, scaling: dict, inv: torch.Tensor) -> torch.Tensor:
+    """Frequencies stretched by ``factor`` where a coordinate turns fewer than ``slow`` times over the
+    ``original`` positions, kept where it turns more than ``fast`` times, blended linearly in between.
+
+    The coordinate whose frequency makes n turns over the original length is
+    c(n) = rotary_dim * ln(original / (2 pi n)) / (2 ln theta); with lo = max(floor(c(fast)), 0) and
+    hi = min(ceil(c(slow)), rotary_dim - 1), coordinate i gets the share m_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)
+    of the stretched frequency: f_i / factor * m_i + f_i * (1 - m_i).  float64."""
+    factor, original = float(scaling["factor"]), float(scaling["original"])
+
+    def coordinate(turns: float) -> float:
+        return rotary_dim * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(theta))
+    lo = max(math.floor(coordinate(float(scaling["fast"]))), 0)
+    hi = min(math.ceil(coordinate(float(scaling["slow"]))), rotary_dim - 1)
+    i = torch.arange(rotary_dim // 2, dtype=torch.float64)
+    share = ((i - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+    return inv / factor * share + inv * (1.0 - share)
+
+
+def table_gain(scaling: Optional[dict]) -> float:
+    """What cos and sin are multiplied by: 0.1 ln(factor) + 1 under yarn scaling, else 1."""
+    if scaling and scaling.get("kind") == "yarn":
+        return 0.1 * math.log(float(scaling["factor"])) + 1.0
+    return 1.0
+
+
 @register_position_encoding("rotary")
 class Rotary:
-    """params: ``head_dim``, ``rotary_dim``, ``theta``, ``max_positions``, ``scaling``, ``pairing``
+    """params: ``head_dim``, ``rotary_dim``, ``theta``, ``max_positions``, ``scaling`` (None, the llama3 keys, or
+    ``{"kind": "yarn", "factor", "original", "fast", "slow"}``, which also scales the tables), ``pairing``
     (``"halves"``: coordinate i turns with i + rotary_dim/2, the default; ``"interleaved"``: 2i with 2i + 1).
 
     Interface of a position encoding: ``encode_and_append(ctx, qkv, kv, n_q, n_kv, write)``
@@ -54,8 +83,9 @@ class Rotary:
         inv = scaled_inverse_frequencies(self.rotary_dim, float(params["theta"]), params.get("scaling"))
         angle = torch.arange(n_pos, dtype=torch.float64, device=build.device)[:, None] \
             * inv.to(build.device)[None, :]
-        self.cos = angle.cos().to(torch.float32).contiguous()
-        self.sin = angle.sin().to(torch.float32).contiguous()
+        gain = table_gain(params.get("scaling"))
+        self.cos = (angle.cos() * gain).to(torch.float32).contiguous()
+        self.sin = (angle.sin() * gain).to(torch.float32).contiguous()
 
     def check_range(self, batch) -> None:
         if batch.max_total > self.max_positions:
