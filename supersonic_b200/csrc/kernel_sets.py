@@ -139,11 +139,11 @@ class PlainKernels:
         ops.head_norm_gate(o, weight, eps, gate, out, n_heads, vdim, pdl=self.pdl, gate_kind=gate_kind)
 
     def state_scan_prepare(self, z, z_bias, decay_kind, decay_scale, n_heads, dim, proj=None, k_off=0, a_off=0,
-                           a_bias=None, unit_eps=0.0, unit=None):
-        """The float32 inputs of a matrix-state recurrence: decays in place of ``z``; unit keys and removal
-        vectors into ``unit`` (see ``ops.state_scan_prepare``)."""
+                           a_bias=None, unit_eps=0.0, unit=None, log_decay=False):
+        """The float32 inputs of a matrix-state recurrence: decays in place of ``z`` (their logarithms for the
+        float32 path's scan); unit keys and removal vectors into ``unit`` (see ``ops.state_scan_prepare``)."""
         ops.state_scan_prepare(z, z_bias, decay_kind, decay_scale, n_heads, dim, proj, k_off, a_off, a_bias, unit_eps,
-                               unit, pdl=self.pdl)
+                               unit, log_decay=log_decay, pdl=self.pdl)
 
     def matrix_state_scan(self, proj, r_off, k_off, v_off, decay, kind, state, batch, out, n_heads, dim, vdim,
                           unit=None, bonus=None):

@@ -482,10 +482,11 @@ STATE_SCAN_KINDS = {"delta": 0, "bonus": 1}
 def state_scan_prepare(z: torch.Tensor, z_bias: torch.Tensor, decay_kind: str, decay_scale: float, n_heads: int,
                        dim: int, proj: Optional[torch.Tensor] = None, k_off: int = 0, a_off: int = 0,
                        a_bias: Optional[torch.Tensor] = None, unit_eps: float = 0.0,
-                       unit: Optional[torch.Tensor] = None, pdl: bool = False) -> None:
+                       unit: Optional[torch.Tensor] = None, log_decay: bool = False, pdl: bool = False) -> None:
     """What a matrix-state recurrence reads besides its projections, in float32.  ``z`` [T, heads x dim] is
     overwritten with the decays: ``"double_exp"``: exp(-exp(z + z_bias)); ``"exp_sigmoid"``:
-    exp(-decay_scale * sigmoid(z + z_bias)).  With ``unit`` [T, 2 x heads x dim]: its first half gets the unit keys
+    exp(-decay_scale * sigmoid(z + z_bias)); with ``log_decay`` their logarithms instead, which is what
+    ``matrix_state_scan`` wants beside float32 projections.  With ``unit`` [T, 2 x heads x dim]: its first half gets the unit keys
     u = k / sqrt(sum_head(k^2) + unit_eps), its second half a * u with a = sigmoid(proj[a_off ..] + a_bias);
     k and the removal's pre-activation are columns of ``proj``."""
     _need(z, "z", torch.float32, 2); _need(z_bias, "z_bias", torch.float32, 1)
@@ -501,7 +502,8 @@ def state_scan_prepare(z: torch.Tensor, z_bias: torch.Tensor, decay_kind: str, d
             raise KernelError("state_scan_prepare: sizes of the unit keys")
         ld, ldu, dt = proj.stride(0), unit.stride(0), dtype_code(proj.dtype)
     _check(_fn("recurrence_ops", "ssb_state_scan_prepare")(
-        _ptr(z), c_int(z.stride(0)), _ptr(z_bias), c_int(DECAY_KINDS[decay_kind]), c_float(decay_scale),
+        _ptr(z), c_int(z.stride(0)), _ptr(z_bias), c_int(DECAY_KINDS[decay_kind]), c_int(1 if log_decay else 0),
+        c_float(decay_scale),
         _ptr(proj if unit is not None else None), c_int(ld), c_int(dt), c_int(k_off), c_int(a_off),
         _ptr(a_bias if unit is not None else None), c_float(unit_eps), _ptr(unit), c_int(ldu), c_int(T), c_int(n_heads),
         c_int(dim), c_int(1 if pdl else 0), _stream()), "state_scan_prepare")
@@ -514,7 +516,8 @@ def matrix_state_scan(proj: torch.Tensor, r_off: int, k_off: int, v_off: int, de
     """Per sequence and head over the sequence's new tokens in order, S [dim, vdim] float32 read from and left in
     ``state[slot]``.  ``"delta"``: S = diag(w) S - (a u)(u^T S) + k v^T, out = S^T r, with ``unit`` = [u | a u] as
     ``state_scan_prepare`` leaves it; ``"bonus"``: out = (S + diag(bonus) k v^T)^T r, then S = diag(w) S + k v^T.
-    ``decay`` [T, heads x dim] float32 holds w; r, k (heads x dim) and v (heads x vdim) are columns of ``proj``."""
+    ``decay`` [T, heads x dim] float32 holds w, or log w if ``proj`` is float32 (that path takes the exponential in
+    double and carries the state of a step's tokens in double); r, k (heads x dim) and v (heads x vdim) are columns of ``proj``."""
     _need(proj, "proj", None, 2); _need(decay, "decay", torch.float32, 2); _need(state, "state", torch.float32, 2)
     _need(out, "out", torch.float32, 2); _need(cu_new, "cu_new", torch.int32, 1); _need(seq_slot, "seq_slot", torch.int32, 1)
     T, B, HD = proj.shape[0], seq_slot.shape[0], n_heads * dim

@@ -10,6 +10,7 @@
 // sum depends on what else is in the batch.
 #include "common.cuh"
 #include <math.h>
+#include <type_traits>
 
 typedef __nv_bfloat16 bf16;
 
@@ -330,12 +331,13 @@ constexpr int MS_TOKENS = 4;         // tokens staged per pair of barriers
 constexpr int MS_THREADS = MS_LANES * MS_COLS;
 
 // Decays in place and, for the delta rule, unit keys and removal vectors.  One block per (token, head).
-//   decay_kind 0: z <- exp(-exp(z + z_bias));  1: z <- exp(-decay_scale * sigmoid(z + z_bias))
+//   decay_kind 0: z <- exp(-exp(z + z_bias));  1: z <- exp(-decay_scale * sigmoid(z + z_bias));
+//   log_decay: z gets the decay's logarithm instead (the float32 path's scan takes the exponential in double)
 //   with_unit: unit[t] = [u | a * u], u = k / sqrt(sum(k^2) + unit_eps), a = sigmoid(a_pre + a_bias)
 template <typename T>
 __global__ void __launch_bounds__(64)
 state_scan_prepare_kernel(float* __restrict__ z, int ldz, const float* __restrict__ z_bias, int decay_kind,
-                          float decay_scale, const T* __restrict__ proj, int ld, int k_off, int a_off,
+                          int log_decay, float decay_scale, const T* __restrict__ proj, int ld, int k_off, int a_off,
                           const float* __restrict__ a_bias, float unit_eps, float* __restrict__ unit, int ldu,
                           int n_heads, int dim) {
     __shared__ float red[64];
@@ -346,7 +348,8 @@ state_scan_prepare_kernel(float* __restrict__ z, int ldz, const float* __restric
     float* zr = z + t * ldz + (size_t)h * dim;
     for (int i = tid; i < dim; i += 64) {
         const float v = zr[i] + z_bias[h * dim + i];
-        zr[i] = decay_kind == 0 ? expf(-expf(v)) : expf(-decay_scale / (1.0f + expf(-v)));
+        const float lw = decay_kind == 0 ? -expf(v) : -decay_scale / (1.0f + expf(-v));
+        zr[i] = log_decay ? lw : expf(lw);
     }
     if (unit == nullptr) return;
     const T* kr = proj + t * ld + k_off + (size_t)h * dim;
@@ -373,7 +376,7 @@ state_scan_prepare_kernel(float* __restrict__ z, int ldz, const float* __restric
     }
 }
 
-SSB_API int ssb_state_scan_prepare(float* z, int ldz, const float* z_bias, int decay_kind, float decay_scale,
+SSB_API int ssb_state_scan_prepare(float* z, int ldz, const float* z_bias, int decay_kind, int log_decay, float decay_scale,
                                    const void* proj, int ld, int dtype, int k_off, int a_off, const float* a_bias,
                                    float unit_eps, float* unit, int ldu, int n_tokens, int n_heads, int dim, int pdl,
                                    cudaStream_t stream) {
@@ -383,10 +386,10 @@ SSB_API int ssb_state_scan_prepare(float* z, int ldz, const float* z_bias, int d
     int rc;
     if (dtype == SSB_F32)
         rc = ssb_launch(state_scan_prepare_kernel<float>, grid, dim3(64), 0, stream, pdl != 0, z, ldz, z_bias, decay_kind,
-                        decay_scale, (const float*)proj, ld, k_off, a_off, a_bias, unit_eps, unit, ldu, n_heads, dim);
+                        log_decay, decay_scale, (const float*)proj, ld, k_off, a_off, a_bias, unit_eps, unit, ldu, n_heads, dim);
     else if (dtype == SSB_BF16)
         rc = ssb_launch(state_scan_prepare_kernel<bf16>, grid, dim3(64), 0, stream, pdl != 0, z, ldz, z_bias, decay_kind,
-                        decay_scale, (const bf16*)proj, ld, k_off, a_off, a_bias, unit_eps, unit, ldu, n_heads, dim);
+                        log_decay, decay_scale, (const bf16*)proj, ld, k_off, a_off, a_bias, unit_eps, unit, ldu, n_heads, dim);
     else
         return SSB_ERR_BAD_DTYPE;
     return rc ? rc : ssb_launch_status();
@@ -418,7 +421,13 @@ matrix_state_scan_kernel(const T* __restrict__ proj, int ld, int r_off, int k_of
     if (t0 >= t1) return;
     const bool col = j0 + cj < vdim;
     float* S = state + ((size_t)slot * n_heads + h) * dim * vdim;
-    float s_reg[RPL], b_reg[RPL];
+    // the float32 path (T = float) carries the state of a step's tokens in double and is given the decays'
+    // logarithms, of which it takes the exponential in double: a decay within 1e-3 of one, rounded to float32,
+    // is off by 1e-4 of its logarithm, the same way at every token if its input hardly changes
+    constexpr bool PRECISE = std::is_same<T, float>::value;
+    using A = typename std::conditional<PRECISE, double, float>::type;
+    A s_reg[RPL];
+    float b_reg[RPL];
 #pragma unroll
     for (int r = 0; r < RPL; ++r) {
         const int i = sub * RPL + r;
@@ -472,57 +481,66 @@ matrix_state_scan_kernel(const T* __restrict__ proj, int ld, int r_off, int k_of
             const float4* w4 = reinterpret_cast<const float4*>(&vec[0][tt][sub * RPL]);
             const float4* k4 = reinterpret_cast<const float4*>(&vec[1][tt][sub * RPL]);
             const float4* r4 = reinterpret_cast<const float4*>(&vec[2][tt][sub * RPL]);
-            float o = 0.f;
+            A o = 0;
+            const float* wv = &vec[0][tt][sub * RPL];
+            const float* kvv = &vec[1][tt][sub * RPL];
+            const float* rv = &vec[2][tt][sub * RPL];
             if (DELTA) {
-                const float4* u4 = reinterpret_cast<const float4*>(&vec[NV - 2][tt][sub * RPL]);
-                const float4* au4 = reinterpret_cast<const float4*>(&vec[NV - 1][tt][sub * RPL]);
-                float seen = 0.f;
+                const float* uv = &vec[NV - 2][tt][sub * RPL];
+                const float* auv = &vec[NV - 1][tt][sub * RPL];
+                A seen = 0;
 #pragma unroll
                 for (int r = 0; r < RPL; r += 4) {
-                    const float4 u = u4[r >> 2];
-                    seen = fmaf(u.x, s_reg[r], seen);
-                    seen = fmaf(u.y, s_reg[r + 1], seen);
-                    seen = fmaf(u.z, s_reg[r + 2], seen);
-                    seen = fmaf(u.w, s_reg[r + 3], seen);
+                    const float4 u = *reinterpret_cast<const float4*>(uv + r);
+                    seen += (A)u.x * s_reg[r] + (A)u.y * s_reg[r + 1] + (A)u.z * s_reg[r + 2] + (A)u.w * s_reg[r + 3];
                 }
                 seen += __shfl_xor_sync(0xffffffffu, seen, 1);
                 seen += __shfl_xor_sync(0xffffffffu, seen, 2);
                 seen += __shfl_xor_sync(0xffffffffu, seen, 4);
 #pragma unroll
                 for (int r = 0; r < RPL; r += 4) {
-                    const float4 w = w4[r >> 2], k = k4[r >> 2], q = r4[r >> 2], au = au4[r >> 2];
-                    s_reg[r] = fmaf(w.x, s_reg[r], fmaf(k.x, v, -au.x * seen));          o = fmaf(s_reg[r], q.x, o);
-                    s_reg[r + 1] = fmaf(w.y, s_reg[r + 1], fmaf(k.y, v, -au.y * seen));  o = fmaf(s_reg[r + 1], q.y, o);
-                    s_reg[r + 2] = fmaf(w.z, s_reg[r + 2], fmaf(k.z, v, -au.z * seen));  o = fmaf(s_reg[r + 2], q.z, o);
-                    s_reg[r + 3] = fmaf(w.w, s_reg[r + 3], fmaf(k.w, v, -au.w * seen));  o = fmaf(s_reg[r + 3], q.w, o);
+                    const float4 w = *reinterpret_cast<const float4*>(wv + r), k = *reinterpret_cast<const float4*>(kvv + r);
+                    const float4 q = *reinterpret_cast<const float4*>(rv + r), au = *reinterpret_cast<const float4*>(auv + r);
+                    const float ww[4] = {w.x, w.y, w.z, w.w}, kk[4] = {k.x, k.y, k.z, k.w};
+                    const float qq[4] = {q.x, q.y, q.z, q.w}, aa[4] = {au.x, au.y, au.z, au.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const A dec = PRECISE ? (A)exp((double)ww[e]) : (A)ww[e];
+                        s_reg[r + e] = dec * s_reg[r + e] + ((A)kk[e] * (A)v - (A)aa[e] * seen);
+                        o += s_reg[r + e] * (A)qq[e];
+                    }
                 }
             } else {
 #pragma unroll
                 for (int r = 0; r < RPL; r += 4) {
-                    const float4 w = w4[r >> 2], k = k4[r >> 2], q = r4[r >> 2];
-                    const float kv0 = k.x * v, kv1 = k.y * v, kv2 = k.z * v, kv3 = k.w * v;
-                    o = fmaf(fmaf(b_reg[r], kv0, s_reg[r]), q.x, o);          s_reg[r] = fmaf(w.x, s_reg[r], kv0);
-                    o = fmaf(fmaf(b_reg[r + 1], kv1, s_reg[r + 1]), q.y, o);  s_reg[r + 1] = fmaf(w.y, s_reg[r + 1], kv1);
-                    o = fmaf(fmaf(b_reg[r + 2], kv2, s_reg[r + 2]), q.z, o);  s_reg[r + 2] = fmaf(w.z, s_reg[r + 2], kv2);
-                    o = fmaf(fmaf(b_reg[r + 3], kv3, s_reg[r + 3]), q.w, o);  s_reg[r + 3] = fmaf(w.w, s_reg[r + 3], kv3);
+                    const float4 w = *reinterpret_cast<const float4*>(wv + r), k = *reinterpret_cast<const float4*>(kvv + r);
+                    const float4 q = *reinterpret_cast<const float4*>(rv + r);
+                    const float ww[4] = {w.x, w.y, w.z, w.w}, kk[4] = {k.x, k.y, k.z, k.w}, qq[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const A dec = PRECISE ? (A)exp((double)ww[e]) : (A)ww[e];
+                        const A kv = (A)kk[e] * (A)v;
+                        o += ((A)b_reg[r + e] * kv + s_reg[r + e]) * (A)qq[e];
+                        s_reg[r + e] = dec * s_reg[r + e] + kv;
+                    }
                 }
             }
             o += __shfl_xor_sync(0xffffffffu, o, 1);
             o += __shfl_xor_sync(0xffffffffu, o, 2);
             o += __shfl_xor_sync(0xffffffffu, o, 4);
-            if (sub == 0 && col) out[(size_t)(t + tt) * ldo + h * vdim + j0 + cj] = o;
+            if (sub == 0 && col) out[(size_t)(t + tt) * ldo + h * vdim + j0 + cj] = (float)o;
         }
         __syncthreads();
     }
 #pragma unroll
     for (int r = 0; r < RPL; ++r) {
         const int i = sub * RPL + r;
-        if (col && i < dim) S[(size_t)i * vdim + j0 + cj] = s_reg[r];
+        if (col && i < dim) S[(size_t)i * vdim + j0 + cj] = (float)s_reg[r];
     }
 }
 
 // proj [T, ld]: r, k (n_heads x dim) and v (n_heads x vdim) from the given columns; decay [T, ldd] float32
-// (n_heads x dim); kind 0 (delta rule): unit [T, ldu] float32 = [u | a * u]; kind 1: bonus [n_heads x dim]
+// (n_heads x dim), for float32 rows their logarithms (what the prepare kernel leaves in either case); kind 0 (delta rule): unit [T, ldu] float32 = [u | a * u]; kind 1: bonus [n_heads x dim]
 // float32 or null; state [slots, n_heads, dim, vdim] float32; out [T, ldo] float32 (n_heads x vdim).
 SSB_API int ssb_matrix_state_scan(const void* proj, int ld, int dtype, int r_off, int k_off, int v_off,
                                   const float* decay, int ldd, int kind, const float* unit, int ldu, const float* bonus,
@@ -578,7 +596,11 @@ gated_unit_scan_kernel(const float* __restrict__ gates, int ldg, const float* __
     const int t0 = cu_new[b], t1 = cu_new[b + 1];
     const int gc = (c / block) * 2 * block + c % block;           // where the channel's g_r sits; g_i is `block` on
     const float br = bias_r[c], bi = bias_i[c], rt = rate[c], yb = y_bias ? y_bias[c] : 0.f;
-    float S = state[(size_t)slot * channels + c];
+    // the float32 path carries the state of a step's tokens in double (it is stored as float32 between steps),
+    // and takes the decay and the input's share in double too: a state that remembers for a thousand tokens
+    // has a decay within 1e-3 of one, whose float32 rounding is a 1e-4 of its logarithm
+    using A = typename std::conditional<std::is_same<T, float>::value, double, float>::type;
+    A S = state[(size_t)slot * channels + c];
     float gr[AHEAD], gi[AHEAD], uu[AHEAD], yy[AHEAD];
     auto fetch = [&](int t) {
 #pragma unroll
@@ -600,15 +622,21 @@ gated_unit_scan_kernel(const float* __restrict__ gates, int ldg, const float* __
 #pragma unroll
         for (int n = 0; n < AHEAD; ++n)
             if (t + n < t1) {
-                const float r = 1.0f / (1.0f + expf(-(cgr[n] + br)));
-                const float i = 1.0f / (1.0f + expf(-(cgi[n] + bi)));
-                const float log_a = rt * r;
-                const float a = expf(log_a);
-                S = fmaf(a, S, sqrtf(-expm1f(2.0f * log_a)) * i * cu[n]);
-                out[(size_t)(t + n) * ldo + c] = ssb_from_float<T>(S * gelu_tanh_f(cy[n] + yb));
+                if (std::is_same<T, float>::value) {
+                    const double r = 1.0 / (1.0 + exp(-((double)cgr[n] + br)));
+                    const double i = 1.0 / (1.0 + exp(-((double)cgi[n] + bi)));
+                    const double log_a = (double)rt * r;
+                    S = fma(exp(log_a), (double)S, sqrt(-expm1(2.0 * log_a)) * i * cu[n]);
+                } else {
+                    const float r = 1.0f / (1.0f + expf(-(cgr[n] + br)));
+                    const float i = 1.0f / (1.0f + expf(-(cgi[n] + bi)));
+                    const float log_a = rt * r;
+                    S = fmaf(expf(log_a), (float)S, sqrtf(-expm1f(2.0f * log_a)) * i * cu[n]);
+                }
+                out[(size_t)(t + n) * ldo + c] = ssb_from_float<T>((float)S * gelu_tanh_f(cy[n] + yb));
             }
     }
-    state[(size_t)slot * channels + c] = S;
+    state[(size_t)slot * channels + c] = (float)S;
 }
 
 SSB_API int ssb_gated_unit_scan(const float* gates, int ldg, const float* bias_r, const float* bias_i, const float* rate,

@@ -153,7 +153,7 @@ class DeltaRule:
         k.linear(proj[:, self.z_off:], self.w2, z)
         unit = torch.empty((T, 2 * HD), dtype=torch.float32, device=dev)
         k.state_scan_prepare(z, self.w0, "exp_sigmoid", self.decay_scale, H, d, proj, self.k_off, self.a_off,
-                             self.a_bias, self.unit_eps, unit)
+                             self.a_bias, self.unit_eps, unit, log_decay=self.dtype == torch.float32)
         o = torch.empty((T, HD), dtype=torch.float32, device=dev)
         k.matrix_state_scan(proj, self.r_off, self.k_off, self.v_off, z, "delta", ctx.cache.state(cache_id), ctx.batch,
                             o, H, d, d, unit=unit)
@@ -218,7 +218,7 @@ class TimeMixing:
         k.tanh_(proj[:, self.z_off:])
         z = torch.empty((T, HD), dtype=torch.float32, device=dev)
         k.linear(proj[:, self.z_off:], self.w2, z)
-        k.state_scan_prepare(z, self.w0, "double_exp", 1.0, H, d)
+        k.state_scan_prepare(z, self.w0, "double_exp", 1.0, H, d, log_decay=self.dtype == torch.float32)
         o = torch.empty((T, HD), dtype=torch.float32, device=dev)
         k.matrix_state_scan(proj, self.r_off, self.k_off, self.v_off, z, "bonus", ctx.cache.state((cache_id, "state")),
                             ctx.batch, o, H, d, d, bonus=self.bonus)

@@ -1,0 +1,421 @@
+"""The Vufadra design in the engine against the plain statement of it (``plain_vufadra``): the operations
+along a sequence and every mixer alone, then whole models through the step function in every way of cutting
+and batching, and generation through the entry point."""
+import copy
+
+import numpy as np
+import pytest
+import torch
+
+import plain_vufadra as pv
+import tiny_vufadra as tv
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def make_model(cfg, store, dtype, max_tokens=1024, **kw):
+    from supersonic_b200.engine import Model
+    return Model.from_config(cfg, store, dtype=dtype, device=DEV, max_tokens=max_tokens, **kw)
+
+
+def run_in_portions(model, tokens, cuts):
+    """Logits of every position [T, vocab] with the sequence fed in portions of the given sizes."""
+    from supersonic_b200.engine import StepEntry
+    slot, at, rows = model.open_sequence(), 0, []
+    for n in cuts:
+        rows.append(model.step([StepEntry(slot, tokens[at:at + n], list(range(n)))]).cpu())
+        at += n
+    assert at == len(tokens)
+    model.close_sequence(slot)
+    model.check_errors()
+    return torch.cat(rows).double()
+
+
+def close(got, ref, dtype, what=""):
+    """float32: a few units of float32 rounding of the logits' size.  bfloat16: the error's root mean square per
+    position against the spread of that position's logits; rounding moves a few positions of these wide-drawn
+    models by more than the typical 1 to 3 % (the plain kernels with bfloat16 storage show the same positions), so
+    the bound is on the typical position, on how many positions are far off, and on the worst one.  The float32
+    runs of the same tests are the sharp ones."""
+    assert torch.isfinite(got).all(), what
+    if dtype == torch.float32:
+        assert float((got - ref).abs().max()) < 2e-4 * max(1.0, float(ref.abs().max())), what
+    else:
+        rel = position_errors(got, ref)
+        assert float(rel.median()) < 0.05 and float((rel > 0.08).double().mean()) <= 0.1 and float(rel.max()) < 0.45, \
+            (what, rel.median(), (rel > 0.08).double().mean(), rel.max())
+
+
+def position_errors(got, ref):
+    return (got - ref).pow(2).mean(-1).sqrt() / ref.std(-1).clamp_min(1e-6)
+
+
+def tokens_of(cfg, n, seed):
+    return np.random.default_rng(seed).integers(0, cfg.vocab, n).tolist()
+
+
+def reference(cfg, plain, tokens):
+    return pv.forward(tokens, plain, cfg.to_dict())[0]
+
+
+# ---- the parts alone ---------------------------------------------------------------------------------
+def part_context(dtype, store, max_positions=600):
+    from supersonic_b200.csrc.kernel_sets import kernel_set_for
+    from supersonic_b200.parts import BuildContext, WeightAccess
+    return BuildContext(torch.device(DEV), dtype, kernel_set_for(dtype), WeightAccess(store, DEV), max_positions)
+
+
+def step_context(build, cache, entries):
+    from supersonic_b200.engine import StepContext, pack_step
+    starts = [cache.length(e.slot) for e in entries]
+    batch = pack_step(entries, starts, DEV)
+    for e in entries:
+        cache.reserve(e.slot, len(e.tokens))
+    cache.sync()
+    return StepContext(batch, cache, build.kernels, build.dtype)
+
+
+def in_pieces(run, need, width, x, pieces, dtype):
+    """What ``run(ctx, rows, out)`` adds into a zeroed ``out`` for one sequence whose rows ``x`` arrive in
+    pieces, through a cache of its own holding ``need`` under id 0."""
+    from supersonic_b200.cache import SequenceCache
+    from supersonic_b200.engine import StepEntry
+    cache = SequenceCache({0: need}, 1024, 1024, dtype, DEV)
+    slot, at, out = cache.acquire(), 0, []
+    for n in pieces:
+        ctx = step_context(build=run.build, cache=cache, entries=[StepEntry(slot, [0] * n)])
+        res = torch.zeros(n, width, device=DEV)
+        run(ctx, x[at:at + n].to(DEV, dtype), res)
+        cache.advance(slot, n)
+        out.append(res.cpu())
+        at += n
+    return torch.cat(out).double()
+
+
+def mixer_alone(kind, spec, position, store, dtype, x, pieces):
+    from supersonic_b200.parts import MIXERS, POSITION_ENCODINGS
+    build = part_context(dtype, store)
+    mixer = MIXERS[kind](spec["params"], spec["weights"], build)
+    pos = None if position is None else POSITION_ENCODINGS[position.kind](position.params, {}, build)
+
+    def run(ctx, rows, out):
+        mixer.forward(ctx, rows, out, 0, True, pos)
+    run.build = build
+    return in_pieces(run, mixer.cache_need(), x.shape[1], x.float(), pieces, dtype)
+
+
+PIECES = [70, 2, 2, 59] + [1] * 17       # crosses page borders; portions of two; then token by token
+T_ALONE = 150
+
+
+def rows_for(cfg, seed, dtype):
+    return torch.randn(T_ALONE, cfg.width, generator=torch.Generator().manual_seed(seed)).to(dtype)
+
+
+def tolerance(dtype, ref, loose=0.04):
+    return (1e-4 if dtype == torch.float32 else loose) * max(1.0, float(ref.abs().max()))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name,layer", [("A", 1), ("B", 2), ("C", 0), ("D", 2)])
+def test_real_gated_recurrence_alone(dtype, name, layer):
+    """One to five taps, one to five gate blocks: the convolution's tail and the state cross every cut."""
+    cfg, store, plain = tv.build(name)
+    spec = cfg.build_spec().blocks[layer].mixer
+    x = rows_for(cfg, layer, dtype)
+    ref = pv.real_gated_recurrence(x.double(), plain, f"l{layer}.mix", cfg.layers[layer]["mixer"])
+    got = mixer_alone("real_gated_recurrence", {"params": spec.params, "weights": spec.weights}, None, store, dtype, x, PIECES)
+    assert float((got - ref).abs().max()) < tolerance(dtype, ref)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name,layer", [("A", 2), ("B", 0), ("C", 2), ("D", 1)])
+def test_delta_rule_alone(dtype, name, layer):
+    cfg, store, plain = tv.build(name)
+    spec = cfg.build_spec().blocks[layer].mixer
+    x = rows_for(cfg, 10 + layer, dtype)
+    ref = pv.generalized_delta(x.double(), plain, f"l{layer}.mix", cfg.layers[layer]["mixer"], cfg.norm_eps)
+    got = mixer_alone("delta_rule", {"params": spec.params, "weights": spec.weights}, None, store, dtype, x, PIECES)
+    assert float((got - ref).abs().max()) < tolerance(dtype, ref, 0.06)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name,layer", [("A", 0), ("B", 1), ("C", 1), ("D", 0)])
+def test_time_mixing_alone(dtype, name, layer):
+    cfg, store, plain = tv.build(name)
+    half = cfg.build_spec().blocks[layer].mixer.params["right"]
+    x = rows_for(cfg, 20 + layer, dtype)
+    ref = pv.time_mixing(x.double(), plain, f"l{layer}.mix.right", cfg.layers[layer]["mixer"]["right"], cfg.norm_eps)
+    got = mixer_alone("time_mixing", half, None, store, dtype, x, PIECES)
+    assert float((got - ref).abs().max()) < tolerance(dtype, ref, 0.06)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name,layer", [("A", 0), ("B", 1), ("C", 1), ("D", 0)])
+def test_sigmoid_attention_alone(dtype, name, layer):
+    """Chunks of 7, 20, 64 and 128 positions against pages of 64: every position of a prompt that crosses
+    chunk and page borders, then portions of two and single tokens (keys just inside and just outside a
+    chunk on both paths); query heads over one, fewer and as many kv heads; partial and whole rotation."""
+    cfg, store, plain = tv.build(name)
+    block = cfg.build_spec().blocks[layer]
+    half = block.mixer.params["left"]
+    x = rows_for(cfg, 30 + layer, dtype)
+    ref = pv.chunked_sigmoid_attention(x.double(), plain, f"l{layer}.mix.left", cfg.layers[layer]["mixer"]["left"], cfg.norm_eps)
+    got = mixer_alone("sigmoid_attention", half, block.position, store, dtype, x, PIECES)
+    assert float((got - ref).abs().max()) < tolerance(dtype, ref)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_mixer_pair_alone(dtype):
+    cfg, store, plain = tv.build("A")
+    block = cfg.build_spec().blocks[0]
+    x = rows_for(cfg, 40, dtype)
+    ref = pv.side_by_side(x.double(), plain, "l0.mix", cfg.layers[0]["mixer"], cfg.norm_eps)
+    got = mixer_alone("mixer_pair", {"params": block.mixer.params, "weights": block.mixer.weights}, block.position, store,
+                      dtype, x, PIECES)
+    assert float((got - ref).abs().max()) < tolerance(dtype, ref)
+
+
+def test_pair_embedding_and_token_shift_in_a_batch_of_portions():
+    """Three sequences whose tokens arrive in unequal portions, several sequences a step: the row picked by the
+    token before (the table's last row for a sequence's first token) and the mix with the row before, across
+    every cut."""
+    from supersonic_b200.cache import SequenceCache, StateNeed
+    from supersonic_b200.csrc.kernel_sets import kernel_set_for
+    from supersonic_b200.engine import StepEntry
+    from supersonic_b200.parts import EMBEDDINGS
+    cfg, store, plain = tv.build("A")
+    dtype = torch.float32
+    build = part_context(dtype, store)
+    spec = cfg.build_spec()
+    emb = EMBEDDINGS["pair_embedding"](spec.embedding.params, spec.embedding.weights, build)
+    cache = SequenceCache({"embedding": emb.cache_need(), 0: StateNeed(cfg.width)}, 1024, 512, dtype, DEV)
+    seqs = [tokens_of(cfg, n, n) for n in (1, 40, 23)]
+    plans = [[1], [17, 1, 2, 20], [2, 1, 1, 19]]
+    slots = [cache.acquire() for _ in seqs]
+    mu = torch.rand(2, cfg.width, generator=torch.Generator().manual_seed(3)).to(DEV)
+    got_e, got_m = [[] for _ in seqs], [[] for _ in seqs]
+    at = [0, 0, 0]
+    for step in range(4):
+        live = [i for i in range(3) if step < len(plans[i])]
+        entries = [StepEntry(slots[i], seqs[i][at[i]:at[i] + plans[i][step]]) for i in live]
+        ctx = step_context(build, cache, entries)
+        rows = emb(ctx, ctx.batch.token_ids)
+        mixed = torch.empty((2,) + tuple(rows.shape), device=DEV)
+        build.kernels.shift_mix(rows, mu, cache.state(0), ctx.batch, mixed)
+        o = 0
+        for i in live:
+            n = plans[i][step]
+            got_e[i].append(rows[o:o + n].cpu())
+            got_m[i].append(mixed[:, o:o + n].cpu())
+            cache.advance(slots[i], n)
+            at[i] += n
+            o += n
+    for i, seq in enumerate(seqs):
+        ref = pv.embedding(seq, plain, cfg.to_dict())
+        assert float((torch.cat(got_e[i]).double() - ref).abs().max()) < 1e-6
+        for s in range(2):
+            want = pv.shifted(ref, mu[s].cpu().double())
+            assert float((torch.cat([m[s] for m in got_m[i]]).double() - want).abs().max()) < 1e-5
+    # a sequence's first token takes the last row of the pair table
+    assert torch.equal(torch.cat(got_e[0])[0], (plain["embed"][seqs[0][0]].float() + plain["bigram"][-1].float()))
+
+
+def test_stream_after_every_layer_run():
+    """float32: the stream after every run of a layer (a looped layer counts each time), the loop's entries
+    with their own vector per pass, and the logits, against the plain statement."""
+    from supersonic_b200.engine import StepEntry
+    for name in ("A", "B", "C", "D"):
+        cfg, store, plain = tv.build(name)
+        model = make_model(cfg, store, torch.float32)
+        tokens = tokens_of(cfg, 70, 3)
+        ref, runs = pv.forward(tokens, plain, cfg.to_dict())
+        seen = []
+        model.layer_probe = lambda stop, x: seen.append(x.cpu().double())
+        slot = model.open_sequence()
+        got = model.step([StepEntry(slot, tokens, list(range(len(tokens))))]).cpu().double()
+        assert len(seen) == runs.shape[0] == len(cfg.layer_order())
+        for i, s in enumerate(seen):
+            assert float((s - runs[i]).abs().max()) < 1e-4 * max(1.0, float(runs[i].abs().max())), (name, i)
+        close(got, ref, torch.float32, name)
+
+
+# ---- whole models through the step function --------------------------------------------------------
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_portions_of_every_size_and_token_by_token(dtype, name):
+    cfg, store, plain = tv.build(name)
+    model = make_model(cfg, store, dtype)
+    T = 140
+    tokens = tokens_of(cfg, T, 5)
+    ref = reference(cfg, plain, tokens)
+    for cuts in ([T], [64, 64, 12], [63, 2, 2, 61, 3, 7, 2], [1] * 6 + [2] * 3 + [128], [100] + [1] * 40, [1] * T):
+        close(run_in_portions(model, tokens, cuts), ref, dtype, (name, cuts))
+    assert model.cache.slots.n_held == 0
+    model.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["C", "D"])
+def test_sizes_that_no_fast_kernel_takes_and_sizes_that_all_take(dtype, name):
+    """Odd widths, ranks and head sizes (every operation on its plain kernel, also in bfloat16) and round ones:
+    a prompt in portions, then decoding, in a batch of two."""
+    from supersonic_b200.engine import StepEntry
+    cfg, store, plain = tv.build(name)
+    model = make_model(cfg, store, dtype)
+    seqs = [tokens_of(cfg, 150, 31), tokens_of(cfg, 70, 32)]
+    refs = [reference(cfg, plain, q) for q in seqs]
+    slots = [model.open_sequence() for _ in seqs]
+    got = [[], []]
+    plan = [((0, 100), (0, 66)), ((100, 130), (66, 68))] + [((130 + i, 131 + i), (68 + i, 69 + i) if i < 2 else None) for i in range(20)]
+    for step in plan:
+        entries = [StepEntry(slots[i], seqs[i][lo_hi[0]:lo_hi[1]], list(range(lo_hi[1] - lo_hi[0])))
+                   for i, lo_hi in enumerate(step) if lo_hi]
+        rows = model.step(entries).cpu().double()
+        at = 0
+        for i, lo_hi in enumerate(step):
+            if lo_hi:
+                got[i].append(rows[at:at + lo_hi[1] - lo_hi[0]])
+                at += lo_hi[1] - lo_hi[0]
+    close(torch.cat(got[0]), refs[0], dtype, name)
+    close(torch.cat(got[1]), refs[1], dtype, name)
+    model.check_errors()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_unequal_batches_against_each_alone_and_reused_slots(dtype):
+    """Five requests of 1 to 131 tokens start together and decode together, the short ones ending first;
+    then other requests run in the slots, pages and state rows those gave back."""
+    from supersonic_b200.engine import StepEntry
+    cfg, store, plain = tv.build("A")
+    model = make_model(cfg, store, dtype, max_tokens=1024)
+    for round_, lens in enumerate(([1, 5, 64, 65, 131], [131, 2, 66], [260, 3, 195, 64], [7, 129, 64, 3])):
+        decode = [3, 9, 14, 6, 11][: len(lens)]
+        seqs = [tokens_of(cfg, n + d, 100 * round_ + i) for i, (n, d) in enumerate(zip(lens, decode))]
+        refs = [reference(cfg, plain, s) for s in seqs]
+        slots = [model.open_sequence() for _ in seqs]
+        got = [[] for _ in seqs]
+        rows = model.step([StepEntry(s, q[:n], list(range(n))) for s, q, n in zip(slots, seqs, lens)]).cpu().double()
+        at = 0
+        for i, n in enumerate(lens):
+            got[i].append(rows[at:at + n])
+            at += n
+        for step in range(max(decode)):
+            live = [i for i in range(len(seqs)) if step < decode[i]]
+            rows = model.step([StepEntry(slots[i], [seqs[i][lens[i] + step]], [0]) for i in live]).cpu().double()
+            for r, i in enumerate(live):
+                got[i].append(rows[r:r + 1])
+            for i in live:
+                if step == decode[i] - 1:
+                    model.close_sequence(slots[i])          # its slot, pages and state go back while the others go on
+        for i in range(len(seqs)):
+            close(torch.cat(got[i]), refs[i], dtype, (round_, i))
+        model.check_errors()
+        assert model.cache.slots.n_held == 0
+        model.cache.check()
+
+
+def sharpened(name, layer):
+    """The configuration's weights changed so that faults show: the attention half's queries scaled up and its
+    per-head offset pushed down, so that a query's output stands on the few keys whose scores are high (a key
+    more or less at a chunk's edge then moves the logits by far more than any tolerance); the recurrent half's
+    and the other layers' decays slowed, so that tokens hundreds of positions back still count."""
+    cfg, store, plain = tv.build(name)
+    p = f"l{layer}.mix"
+    changes = {f"{p}.left.q": plain[f"{p}.left.q"].float() * 6.0,
+               f"{p}.left.pb": torch.full_like(plain[f"{p}.left.pb"].float(), -4.0),
+               f"{p}.right.w0": plain[f"{p}.right.w0"].float() - 5.0}
+    for i, l in enumerate(cfg.layers):
+        if l["type"] == "general_delta":
+            changes[f"l{i}.mix.w0"] = plain[f"l{i}.mix.w0"].float() - 6.0
+        if l["type"] == "rglru":
+            changes[f"l{i}.mix.lam"] = plain[f"l{i}.mix.lam"].float() - 4.0
+    store, plain = tv.changed(plain, **changes)
+    return cfg, store, plain
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_chunk_edges_far_tokens_page_borders_and_first_tokens_show(dtype):
+    cfg, store, plain = sharpened("A", 0)
+    T = 330
+    tokens = tokens_of(cfg, T, 9)
+    ref = reference(cfg, plain, tokens)
+    # the test is sharp.  A chunk one position longer gives other logits right behind every edge ...
+    longer = copy.deepcopy(cfg.to_dict())
+    longer["layers"][0]["mixer"]["left"]["mask"]["size"] += 1
+    other = position_errors(pv.forward(tokens, plain, longer)[0], ref)
+    assert float((other > 0.08).double().mean()) > 0.5 and float(other.median()) > 0.1
+    # ... and a sequence that has lost what came 200 and more positions before gives other logits at its end
+    tail = position_errors(pv.forward(tokens[200:], plain, cfg.to_dict())[0], ref[200:])
+    assert float(tail[-30:].min()) > 0.3
+    model = make_model(cfg, store, dtype)
+    # cuts at chunk edges (20, 40), one before and one behind them, at page borders (64, 128), and decoding across both
+    for cuts in ([T], [1, 1, 1, 16, 1, 1, 1, 18, 1, 1, 22, 1, 63, 1, 1, 200], [19, 2, 19, 2, 21, 1, 64] + [1] * 202, [256] + [1] * 74):
+        close(run_in_portions(model, tokens, cuts), ref, dtype, cuts)
+
+
+def test_long_decoding_keeps_every_state():
+    """300 tokens decoded one by one after a prompt of two, in float32 and with slow decays: the matrices, the
+    vector state, the convolution's tail, the shifted rows and the token before are carried over hundreds of steps."""
+    cfg, store, plain = sharpened("A", 0)
+    model = make_model(cfg, store, torch.float32)
+    tokens = tokens_of(cfg, 302, 21)
+    close(run_in_portions(model, tokens, [2] + [1] * 300), reference(cfg, plain, tokens), torch.float32)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_greedy_generation_through_the_entry_point(dtype):
+    """Prompts of unequal lengths in batches of three through ``Engine.generate`` (its scheduler, cache and
+    sampler): the tokens are those the plain statement picks greedily, and in bfloat16 every picked token
+    is the plain statement's first or close second choice."""
+    from supersonic_b200.api import Engine
+    cfg, store, plain = tv.build("A")
+    model = make_model(cfg, store, dtype, max_tokens=1024, max_seq_tokens=128)
+    prompts = [tokens_of(cfg, n, 40 + n) for n in (1, 9, 64, 17, 70)]
+    out = Engine(model).generate(prompts, max_new_tokens=10, temperature=0.0, ignore_eos=True, batch_size=3)
+    assert [len(o) for o in out] == [10] * len(prompts)
+    for prompt, new in zip(prompts, out):
+        seq = list(prompt)
+        for tok in new:
+            logits = reference(cfg, plain, seq)[-1]
+            if dtype == torch.float32:
+                assert tok == int(logits.argmax())
+            else:
+                assert float(logits.max() - logits[tok]) < 0.05 * float(logits.std())
+            seq.append(tok)
+    assert model.cache.slots.n_held == 0
+
+
+def test_trace_replay_of_a_model_folder(tmp_path):
+    """``bin/trace_run`` on a written folder (decay ranks left to the tensors' shapes): a batch of two prompts, decode
+    steps, and a third request in a freed slot, logits against the plain statement."""
+    import json, os, subprocess, sys
+    from supersonic_b200.weights import WeightStore, write_model_folder
+    cfg, _, _ = tv.build("A")
+    folder = write_model_folder(cfg, 3, str(tmp_path / "m"), std=0.15)
+    d = json.load(open(folder + "/config.json"))
+    d["layers"][2]["mixer"].pop("decay_rank")
+    d["layers"][0]["mixer"]["right"].pop("decay_rank")
+    json.dump(d, open(folder + "/config.json", "w"))
+    st = WeightStore.from_dir(folder)
+    plain = {n: st.get(n) for n in st.names()}
+    a, b, c = tokens_of(cfg, 70, 1), tokens_of(cfg, 5, 2), tokens_of(cfg, 9, 3)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:66], "want": [0, 65]}, {"id": "b", "tokens": b[:3], "want": [2]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": a[66:67], "want": [0]}, {"id": "b", "tokens": b[3:4], "want": []}], "end": []},
+             {"step": 2, "entries": [{"id": "a", "tokens": a[67:68], "want": [0]}, {"id": "b", "tokens": b[4:5], "want": [0]}], "end": ["b"]},
+             {"step": 3, "entries": [{"id": "a", "tokens": a[68:70], "want": [1]}], "end": ["a"]},
+             {"step": 4, "entries": [{"id": "c", "tokens": c, "want": [8]}], "end": ["c"]}]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = tmp_path / "out"
+    r = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", folder, "--dtype", "float32",
+                        "--out", str(out), "--max-tokens", "256"], input="\n".join(json.dumps(s) for s in steps) + "\n",
+                       capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [l for l in r.stdout.splitlines() if l.startswith("done")] == [f"done {i}" for i in range(5)]
+    ra, rb, rc = (reference(cfg, plain, s) for s in (a, b, c))
+    want = {0: torch.cat([ra[[0, 65]], rb[[2]]]), 1: ra[[66]], 2: torch.cat([ra[[67]], rb[[4]]]), 3: ra[[69]], 4: rc[[8]]}
+    for i, ref in want.items():
+        got = torch.from_numpy(np.fromfile(out / f"{i}.f32", dtype="<f4").reshape(-1, cfg.vocab)).double()
+        close(got, ref, torch.float32, i)
