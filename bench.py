@@ -299,6 +299,42 @@ def _sotavik_sizes(name):
     return sot, lla
 
 
+def _vufadra_sizes(name):
+    """(Vufadra config.json, the Llama configuration of the same width, layer count, feed-forward and vocabulary).
+    One of each mixer plus a second delta-rule layer; the loop covers all layers and is walked once, so that the
+    depth is the Llama model's."""
+    def rglru(width, blocks):
+        return {"type": "rglru", "mixer": {"width": width, "conv": 4, "blocks": blocks}}
+
+    def delta(heads, dim):
+        return {"type": "general_delta", "mixer": {"heads": heads, "dim": dim, "decay_rank": 64}}
+
+    def pair(heads, kv, dim, chunk, r_heads, r_dim):
+        return {"type": "parallel", "mixer": {
+            "left": {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "mask": {"size": chunk}, "scale": dim ** -0.5,
+                     "rot": {"base": 10000.0, "dims": dim // 2,
+                             "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}},
+            "right": {"heads": r_heads, "dim": r_dim, "decay_rank": 64}}}
+    if name == "2048":
+        width, vocab, ff = 2048, 32000, 8192
+        mixers = [rglru(2048, 16), delta(32, 64), pair(16, 4, 128, 512, 32, 64), delta(32, 64)]
+        llama = dict(num_attention_heads=32, num_key_value_heads=8, head_dim=64, intermediate_size=ff)
+    elif name == "1024":
+        width, vocab, ff = 1024, 32000, 4096
+        mixers = [rglru(1024, 8), delta(16, 64), pair(8, 2, 128, 256, 16, 64), delta(16, 64)]
+        llama = dict(num_attention_heads=16, num_key_value_heads=4, head_dim=64, intermediate_size=ff)
+    else:
+        raise SystemExit(f"--design-size {name!r}: known sizes are 1024 and 2048")
+    layers = [dict(m, mlp={"kind": "dense", "ff": ff}) for m in mixers]
+    vuf = {"architecture": "Vufadra", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
+           "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31337, "mul_cur": 7919}},
+           "loop": {"start": 0, "stop": len(layers), "times": 1}, "layers": layers}
+    lla = dict(architectures=["LlamaForCausalLM"], vocab_size=vocab, hidden_size=width, num_hidden_layers=len(layers),
+               max_position_embeddings=32768, rms_norm_eps=1e-5, rope_theta=10000.0, rope_scaling=None,
+               tie_word_embeddings=False, **llama)
+    return vuf, lla
+
+
 def _operation_work(model, tokens):
     """Algorithmic work of one prompt of ``tokens`` tokens per operation of the model's parts: (FLOPs, bytes).
     Matrix products count 2 per multiply-add; attention counts its scores and weighted sums over the causal
@@ -320,6 +356,29 @@ def _operation_work(model, tokens):
             add("mixer.linear", 2 * T * (m.w_in.numel() + m.w_a2.numel() + m.w_o.numel()))
             add("mixer.gated_linear_scan", 4 * T * m.H * m.dim * m.vdim,
                 T * (2 * (2 * m.H * m.dim + m.H * m.vdim) + 4 * (m.H * m.dim + m.H * m.vdim)))
+        elif kind == "RealGatedRecurrence":
+            add("mixer.linear", 2 * T * (m.w_in.numel() + m.w_o.numel()))
+            add("mixer.head_linear", 2 * T * m.w_gates.numel())
+            add("mixer.gated_unit_scan", 12 * T * m.C, T * m.C * (8 + 3 * 2))          # gates, u, y in; the gated state out
+            add("mixer.causal_conv", 2 * T * m.C * m.taps, T * m.C * 4)
+        elif kind == "DeltaRule":
+            HD = m.H * m.dim
+            add("mixer.linear", 2 * T * (m.w_in.numel() + m.w2.numel() + m.w_o.numel()))
+            # per state element and token: u^T S, the update's three terms, S^T r; r, k, v in 16 bits, decays and
+            # unit keys in 32, o out in 32
+            add("mixer.matrix_state_scan", 8 * T * HD * m.dim, T * HD * (3 * 2 + 3 * 4 + 4))
+        elif kind == "MixerPair":
+            for _, half, _ in m.halves:
+                hk = type(half).__name__
+                if hk == "SigmoidAttention":
+                    add("mixer.linear", 2 * T * (half.w_qkv.numel() + half.w_o.numel()))
+                    c = int(half.chunk or T)
+                    pairs = (T // c) * (c * (c + 1) // 2) + (T % c) * (T % c + 1) // 2
+                    add("mixer.sigmoid_attention", 2 * pairs * half.n_q * (half.dim + half.vdim))
+                elif hk == "TimeMixing":
+                    HD = half.H * half.dim
+                    add("mixer.linear", 2 * T * (sum(w.numel() for w in half.w) + half.w2.numel() + half.w_o.numel()))
+                    add("mixer.matrix_state_scan", 6 * T * HD * half.dim, T * HD * (3 * 2 + 4 + 4))
         elif kind == "Attention":
             add("mixer.linear", 2 * T * (m.w_qkv.numel() + m.w_o.numel()))
             add("mixer.project_rope_append", 2 * T * m.w_qkv.numel())
@@ -339,21 +398,21 @@ def _operation_work(model, tokens):
 
 
 def design_comparison(args):
-    """``--design sotavik``: prompts and decode steps of the Sotavik design at sizes that resemble a real
-    model's layers, beside a Llama model of the same width and depth, both with random bfloat16 weights;
+    """``--design sotavik`` / ``--design vufadra``: prompts and decode steps of that design at sizes that resemble a
+    real model's layers, beside a Llama model of the same width and depth, both with random bfloat16 weights;
     and for a prompt, the device time of every operation of the parts against its own roofline."""
     import torch
     from supersonic_b200.config import config_from_dict
     from supersonic_b200.engine import Model, StepEntry
     from supersonic_b200.weights import RandomWeightStore
     pk, pk_src = peaks()
-    sot, lla = _sotavik_sizes(args.design_size)
-    out = {"metric": "design_comparison", "design": "sotavik", "beside": "llama", "size": args.design_size,
+    sot, lla = (_vufadra_sizes if args.design == "vufadra" else _sotavik_sizes)(args.design_size)
+    out = {"metric": "design_comparison", "design": args.design, "beside": "llama", "size": args.design_size,
            "layers": len(sot["layers"]), "dtype": "bf16", "data": "synthetic", "peaks": pk, "peaks_source": pk_src,
            "models": {}}
     clocks = ClockSampler()
     clocks.start()
-    for name, d in (("sotavik", sot), ("llama", lla)):
+    for name, d in ((args.design, sot), ("llama", lla)):
         cfg = config_from_dict(d)
         store = RandomWeightStore(cfg, seed=3, device="cuda:0", std=0.02, norm_jitter=0.0)
         ctx = max(args.prefill_tokens, args.prompt_len) + 256
@@ -521,7 +580,7 @@ def main():
                     help="also time decode and prompts at further sizes (adds a 'sweep' key to the line)")
     ap.add_argument("--deterministic", action="store_true",
                     help="time the bfloat16 path without float atomics and with one kernel choice whatever the batch")
-    ap.add_argument("--design", default=None, choices=["sotavik"],
+    ap.add_argument("--design", default=None, choices=["sotavik", "vufadra"],
                     help="instead of the headline workload: this design beside the closest existing model at equal size")
     ap.add_argument("--design-size", default="2048", help="width of the compared models: 1024 or 2048")
     args = ap.parse_args()

@@ -227,6 +227,73 @@ def gated_linear_scan(args):
             "us": round(us, 2), "float32 GFLOP/s": round(4.0 * T * H * d * dv / us / 1e3, 1)}
 
 
+def matrix_state_scan(args):
+    """The delta-rule (--kernel delta) or bonus (--kernel bonus) recurrence over --seqs prompts of --tokens tokens:
+    --heads heads with a state of --k x --k."""
+    H, d, T, B = args.heads, args.k, args.tokens, args.seqs
+    kind = "bonus" if args.kernel == "bonus" else "delta"
+    proj = (torch.randn(B * T, 3 * H * d, device=DEV) * 0.5).bfloat16()
+    decay = torch.rand(B * T, H * d, device=DEV) * 0.1 + 0.9
+    unit = torch.randn(B * T, 2 * H * d, device=DEV) * d ** -0.5
+    bonus = torch.randn(H * d, device=DEV) * 0.3
+    state = torch.zeros(B + 1, H * d * d, device=DEV)
+    cu = torch.arange(0, (B + 1) * T, T, dtype=torch.int32, device=DEV)
+    slots = torch.arange(1, B + 1, dtype=torch.int32, device=DEV)
+    out = torch.zeros(B * T, H * d, device=DEV)
+    us = _time(lambda i: ops.matrix_state_scan(proj, 0, H * d, 2 * H * d, decay, kind, state, cu, slots, out, H, d, d,
+                                               unit=unit if kind == "delta" else None,
+                                               bonus=bonus if kind == "bonus" else None), args.iters)
+    fma = 4 if kind == "delta" else 3
+    return {"kernel": "matrix_state_scan", "kind": kind, "seqs": B, "tokens": T, "heads": H, "dim": d, "us": round(us, 2),
+            "float32 GFLOP/s": round(2.0 * fma * B * T * H * d * d / us / 1e3, 1)}
+
+
+def gated_unit_scan(args):
+    """The vector-state recurrence over --seqs prompts of --tokens tokens and --n channels in blocks of --k."""
+    C, T, B, bs = args.n, args.tokens, args.seqs, args.k
+    gates = torch.randn(B * T, 2 * C, device=DEV)
+    u, y = (torch.randn(B * T, C, device=DEV).bfloat16() for _ in range(2))
+    br, bi, yb = (torch.randn(C, device=DEV) for _ in range(3))
+    rate = -8.0 * torch.rand(C, device=DEV)
+    state = torch.zeros(B + 1, C, device=DEV)
+    cu = torch.arange(0, (B + 1) * T, T, dtype=torch.int32, device=DEV)
+    slots = torch.arange(1, B + 1, dtype=torch.int32, device=DEV)
+    out = torch.empty(B * T, C, device=DEV, dtype=torch.bfloat16)
+    us = _time(lambda i: ops.gated_unit_scan(gates, br, bi, rate, u, y, yb, state, cu, slots, out, bs, max_new=T), args.iters)
+    return {"kernel": "gated_unit_scan", "seqs": B, "tokens": T, "channels": C, "us": round(us, 2),
+            "GB/s": round(B * T * C * 14 / us / 1e3, 1)}
+
+
+def sigmoid_attention(args):
+    """Attention with sigmoid weights in chunks of --chunk positions: --seqs prompts of --tokens tokens (or, with
+    --tokens 1, decode steps at --context), --heads over --kv-heads heads of --head-dim."""
+    H, G, d, B, T, ps = args.heads, args.kv_heads, args.head_dim, args.seqs, args.tokens, 6
+    ctx = args.context if T == 1 else T
+    pages = -(-ctx // 64)
+    kc = (torch.randn(B * pages + 1, G, 64, d, device=DEV) * 0.5).bfloat16()
+    vc = (torch.randn(B * pages + 1, G, 64, d, device=DEV) * 0.5).bfloat16()
+    table = (torch.arange(B * pages, dtype=torch.int32, device=DEV) + 1).view(B, pages).contiguous()
+    q = (torch.randn(B * T, H * d, device=DEV) * 0.5).bfloat16()
+    start = ctx - T
+    pos = (torch.arange(T, dtype=torch.int32, device=DEV) + start).repeat(B)
+    slot = torch.arange(B, dtype=torch.int32, device=DEV).repeat_interleave(T)
+    cu = torch.arange(0, (B + 1) * T, T, dtype=torch.int32, device=DEV)
+    seq_start = torch.full((B,), start, dtype=torch.int32, device=DEV)
+    seq_slot = torch.arange(B, dtype=torch.int32, device=DEV)
+    bias = torch.randn(H, device=DEV)
+    out = torch.empty(B * T, H * d, device=DEV, dtype=torch.bfloat16)
+    c = args.chunk
+    if args.kernel == "plain":
+        fn = lambda i: ops.sigmoid_attention_plain(q, kc, vc, pos, slot, table, bias, out, H, G, d, d, ps, c, None, d ** -0.5)
+    else:
+        fn = lambda i: ops.sigmoid_attention_mma(q, kc, vc, cu, seq_start, seq_slot, table, bias, out, T, H, G, d, d, ps, c,
+                                                 None, d ** -0.5)
+    us = _time(fn, args.iters)
+    pairs = sum(min(p % c, p - start) + 1 if c else p + 1 for p in range(start, ctx)) * B
+    return {"kernel": "sigmoid_attention_" + ("plain" if args.kernel == "plain" else "mma"), "seqs": B, "tokens": T,
+            "context": ctx, "chunk": c, "us": round(us, 2), "TFLOP/s": round(4.0 * pairs * H * d / us / 1e6, 2)}
+
+
 def sampling(args):
     """The pick of a step: argmax at temperature 0, else a draw under the given cuts.  Eight sets of
     logits in turn (64 rows of 128,256 are 33 MB each)."""
@@ -249,7 +316,7 @@ def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     sub = ap.add_subparsers(dest="what", required=True)
     for name in ("attention_decode", "linear", "gemm", "attention_prefill", "sampling", "latent_attention", "grouped_gemm",
-                 "gated_linear_scan"):
+                 "gated_linear_scan", "matrix_state_scan", "gated_unit_scan", "sigmoid_attention"):
         p = sub.add_parser(name)
         p.add_argument("--iters", type=int, default=20)
         p.add_argument("--heads", type=int, default=32)
@@ -281,7 +348,7 @@ def main(argv=None):
         p.add_argument("--form", type=int, default=0, help="latent_attention: warps of a block as 1 x 8, 2 x 4, 2 x 8 (1, 2, 3)")
         p.add_argument("--experts", type=int, default=64)
         p.add_argument("--top", type=int, default=6)
-        p.add_argument("--chunk", type=int, default=128, help="gated_linear_scan: tokens a chunk (0: in one go)")
+        p.add_argument("--chunk", type=int, default=128, help="gated_linear_scan: tokens a chunk (0: in one go); sigmoid_attention: positions a chunk")
     args = ap.parse_args(argv)
     print(json.dumps(globals()[args.what](args)))
 

@@ -355,6 +355,16 @@ class FastKernels(PlainKernels):
                                  page_table, out, sinks, batch.max_new, n_heads, dk, kv_rank, page_shift, window,
                                  scale, splits, partial, pdl=self.pdl)
 
+    def sigmoid_attention(self, q, k_cache, v_cache, batch, page_table, bias, out, n_q, n_kv, dim, vdim, page_shift,
+                          chunk, window, scale):
+        if ops.sigmoid_attention_mma_ok(q, k_cache, v_cache, out, dim, vdim, page_shift):
+            ops.sigmoid_attention_mma(q, k_cache, v_cache, batch.cu_new, batch.seq_start, batch.seq_slot, page_table, bias,
+                                      out, batch.max_new, n_q, n_kv, dim, vdim, page_shift, chunk, window, scale,
+                                      pdl=self._chain(batch.n_tokens))
+        else:
+            super().sigmoid_attention(q, k_cache, v_cache, batch, page_table, bias, out, n_q, n_kv, dim, vdim, page_shift,
+                                      chunk, window, scale)
+
     def gated_linear_scan(self, proj, q_off, k_off, v_off, z, z_bias, tau, q_scale, state, batch, out, n_heads,
                           dim, vdim):
         chunk, n_sums, n_decays = ops.scan_chunking(batch.n_seqs, batch.max_new, n_heads, dim, vdim)

@@ -55,6 +55,12 @@ class PlainKernels:
     name = "plain"
     capturable = False      # the float32 path launches every step eagerly: each launch's status is looked at
     pdl = False             # no launch is a programmatic dependent of the one before
+    PDL_MAX_ROWS = 128      # ... and in a set that does chain its launches, only those of small steps are: the blocks of a
+                            # dependent kernel become resident while a long kernel before it still runs, and a prompt of
+                            # 2,048 tokens whose recurrences take a millisecond each ran 8.1 ms chained and 5.1 ms unchained
+
+    def _chain(self, rows) -> bool:
+        return bool(self.pdl) and int(rows) <= self.PDL_MAX_ROWS
 
     def embed(self, ids, table, out):
         ops.embed(ids, table, out)
@@ -136,49 +142,50 @@ class PlainKernels:
                               sums=sums, decays=decays)
 
     def head_norm_gate(self, o, weight, eps, gate, out, n_heads, vdim, gate_kind="silu"):
-        ops.head_norm_gate(o, weight, eps, gate, out, n_heads, vdim, pdl=self.pdl, gate_kind=gate_kind)
+        ops.head_norm_gate(o, weight, eps, gate, out, n_heads, vdim, pdl=self._chain(o.shape[0]), gate_kind=gate_kind)
 
     def state_scan_prepare(self, z, z_bias, decay_kind, decay_scale, n_heads, dim, proj=None, k_off=0, a_off=0,
                            a_bias=None, unit_eps=0.0, unit=None, log_decay=False):
         """The float32 inputs of a matrix-state recurrence: decays in place of ``z`` (their logarithms for the
         float32 path's scan); unit keys and removal vectors into ``unit`` (see ``ops.state_scan_prepare``)."""
         ops.state_scan_prepare(z, z_bias, decay_kind, decay_scale, n_heads, dim, proj, k_off, a_off, a_bias, unit_eps,
-                               unit, log_decay=log_decay, pdl=self.pdl)
+                               unit, log_decay=log_decay, pdl=self._chain(z.shape[0]))
 
     def matrix_state_scan(self, proj, r_off, k_off, v_off, decay, kind, state, batch, out, n_heads, dim, vdim,
                           unit=None, bonus=None):
         """``kind`` ``"delta"`` (decay, removal along the unit key, then the new pair) or ``"bonus"`` (decay, with
         the token at hand read through a bonus), over every sequence's new tokens from and into its state."""
         ops.matrix_state_scan(proj, r_off, k_off, v_off, decay, kind, state, batch.cu_new, batch.seq_slot, out,
-                              n_heads, dim, vdim, unit=unit, bonus=bonus, pdl=self.pdl)
+                              n_heads, dim, vdim, unit=unit, bonus=bonus, pdl=self._chain(batch.n_tokens))
 
     def gated_unit_scan(self, gates, bias_r, bias_i, rate, u, y, y_bias, state, batch, out, block):
         ops.gated_unit_scan(gates, bias_r, bias_i, rate, u, y, y_bias, state, batch.cu_new, batch.seq_slot, out, block,
-                            pdl=self.pdl)
+                            max_new=batch.max_new, pdl=self._chain(batch.n_tokens))
 
     # ---- along a sequence --------------------------------------------------------------
     def pair_embed(self, ids, table, pair, prev, batch, out, buckets, mul_prev, mul_cur):
         ops.pair_embed(ids, table, pair, prev, batch.cu_new, batch.seq_slot, out, batch.max_new, buckets, mul_prev,
-                       mul_cur, pdl=self.pdl)
+                       mul_cur, pdl=self._chain(batch.n_tokens))
 
     def dynamic_tanh(self, x, alpha, weight, bias, out, rows=None):
-        ops.dynamic_tanh(x, alpha, weight, bias, out, rows, pdl=self.pdl and out.shape[0] <= 64)
+        ops.dynamic_tanh(x, alpha, weight, bias, out, rows, pdl=self._chain(out.shape[0]))
 
     def shift_mix(self, h, mu, last, batch, out):
         """out[s] = h + (h shifted by one token - h) * mu[s]; ``last`` carries a sequence's last row across steps."""
-        ops.shift_mix(h, mu, last, batch.cu_new, batch.seq_slot, out, batch.max_new, pdl=self.pdl)
+        ops.shift_mix(h, mu, last, batch.cu_new, batch.seq_slot, out, batch.max_new, pdl=self._chain(batch.n_tokens))
 
     def causal_conv(self, x, x_bias, weight, bias, tail, batch, out):
-        ops.causal_conv(x, x_bias, weight, bias, tail, batch.cu_new, batch.seq_slot, out, batch.max_new, pdl=self.pdl)
+        ops.causal_conv(x, x_bias, weight, bias, tail, batch.cu_new, batch.seq_slot, out, batch.max_new,
+                        pdl=self._chain(batch.n_tokens))
 
     def concat_cast(self, x, x0, act, bias, out):
-        ops.concat_cast(x, x0, act, bias, out, pdl=self.pdl)
+        ops.concat_cast(x, x0, act, bias, out, pdl=self._chain(x.shape[0]))
 
     def rms_pair_add(self, residual, a, wa, b, wb, eps, scale):
-        ops.rms_pair_add(residual, a, wa, b, wb, eps, scale, pdl=self.pdl)
+        ops.rms_pair_add(residual, a, wa, b, wb, eps, scale, pdl=self._chain(residual.shape[0]))
 
     def tanh_(self, x):
-        ops.tanh_(x, pdl=self.pdl)
+        ops.tanh_(x, pdl=self._chain(x.shape[0]))
 
     # ---- attention with sigmoid weights --------------------------------------------------
     def qk_norm_rope_append(self, qkv, q_weight, k_weight, eps, position, kv, batch, n_q, n_kv, dim, vdim, page_shift,
@@ -191,12 +198,12 @@ class PlainKernels:
             cos, sin, rot_dims = position.rotary_tables()
         k_cache, v_cache, table, _ = kv
         ops.qk_norm_rope_append(qkv, q_weight, k_weight, eps, cos, sin, batch.pos, batch.slot_of_token, table, k_cache,
-                                v_cache, n_q, n_kv, dim, vdim, rot_dims, page_shift, write_cache, pdl=self.pdl)
+                                v_cache, n_q, n_kv, dim, vdim, rot_dims, page_shift, write_cache, pdl=self._chain(batch.n_tokens))
 
     def sigmoid_attention(self, q, k_cache, v_cache, batch, page_table, bias, out, n_q, n_kv, dim, vdim, page_shift,
                           chunk, window, scale):
         ops.sigmoid_attention_plain(q, k_cache, v_cache, batch.pos, batch.slot_of_token, page_table, bias, out, n_q,
-                                    n_kv, dim, vdim, page_shift, chunk, window, scale, pdl=self.pdl)
+                                    n_kv, dim, vdim, page_shift, chunk, window, scale, pdl=self._chain(batch.n_tokens))
 
     # ---- experts ---------------------------------------------------------------------
     expert_tile_rows = 64

@@ -542,13 +542,18 @@ def matrix_state_scan(proj: torch.Tensor, r_off: int, k_off: int, v_off: int, de
         _stream()), "matrix_state_scan")
 
 
+GATED_UNIT_SPLIT_MIN_NEW = 16    # runs of new tokens from which the vector-state recurrence takes its two-launch form
+
+
 def gated_unit_scan(gates: torch.Tensor, bias_r: torch.Tensor, bias_i: torch.Tensor, rate: torch.Tensor,
                     u: torch.Tensor, y: torch.Tensor, y_bias: Optional[torch.Tensor], state: torch.Tensor,
                     cu_new: torch.Tensor, seq_slot: torch.Tensor, out: torch.Tensor, block: int,
-                    pdl: bool = False) -> None:
+                    max_new: int = 1, pdl: bool = False) -> None:
     """Per sequence and channel over the new tokens: r = sigmoid(g_r + bias_r), i = sigmoid(g_i + bias_i),
     a = exp(rate * r), S = a S + sqrt(1 - a^2) i u, out = S * gelu_tanh(y + y_bias).  ``gates`` [T, 2 x channels]
-    float32 holds [g_r | g_i] per block of ``block`` channels; S float32 lives in ``state[slot]``."""
+    float32 holds [g_r | g_i] per block of ``block`` channels; S float32 lives in ``state[slot]``.  Runs of
+    ``GATED_UNIT_SPLIT_MIN_NEW`` and more new tokens in bfloat16 take two launches: what does not depend on the state
+    for all tokens at once (written over ``gates``), then a walk of one multiply-add a token."""
     _need(gates, "gates", torch.float32, 2); _need(u, "u", None, 2); _need(y, "y", u.dtype, 2); _need(out, "out", u.dtype, 2)
     _need(state, "state", torch.float32, 2)
     C = state.shape[1]
@@ -560,6 +565,13 @@ def gated_unit_scan(gates: torch.Tensor, bias_r: torch.Tensor, bias_i: torch.Ten
     if gates.shape[0] != T or gates.shape[1] < 2 * C or min(u.shape[1], y.shape[1], out.shape[1]) < C or y.shape[0] != T \
             or out.shape[0] != T or cu_new.shape[0] != B + 1 or C % block or not state.is_contiguous():
         raise KernelError("gated_unit_scan: sizes")
+    if u.dtype == torch.bfloat16 and max_new >= GATED_UNIT_SPLIT_MIN_NEW:
+        _check(_fn("recurrence_ops", "ssb_gated_unit_scan_split")(
+            _ptr(gates), c_int(gates.stride(0)), _ptr(bias_r), _ptr(bias_i), _ptr(rate), _ptr(u), c_int(u.stride(0)),
+            _ptr(y), c_int(y.stride(0)), _ptr(y_bias), _ptr(state), _ptr(cu_new), _ptr(seq_slot), _ptr(out),
+            c_int(out.stride(0)), c_int(B), c_int(T), c_int(C), c_int(block), c_int(1 if pdl else 0), _stream()),
+            "gated_unit_scan_split")
+        return
     _check(_fn("recurrence_ops", "ssb_gated_unit_scan")(
         _ptr(gates), c_int(gates.stride(0)), _ptr(bias_r), _ptr(bias_i), _ptr(rate), _ptr(u), c_int(u.stride(0)),
         _ptr(y), c_int(y.stride(0)), _ptr(y_bias), _ptr(state), _ptr(cu_new), _ptr(seq_slot), _ptr(out),
@@ -722,6 +734,48 @@ def qk_norm_rope_append(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_w
         _ptr(cos), _ptr(sin), c_int(positions), _ptr(pos), _ptr(slot), _ptr(page_table), c_int(page_table.shape[1]),
         _ptr(k_cache), _ptr(v_cache), c_int(T), c_int(n_q), c_int(n_kv), c_int(dim), c_int(vdim), c_int(rot_dims),
         c_int(page_shift), c_int(1 if write_cache else 0), c_int(1 if pdl else 0), _stream()), "qk_norm_rope_append")
+
+
+SIGMOID_MMA_DIMS = {(64, 64), (64, 128), (96, 64), (96, 96), (128, 64), (128, 128)}
+
+
+def sigmoid_attention_mma_ok(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor, dim: int,
+                             vdim: int, page_shift: int) -> bool:
+    return (q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and v_cache.dtype == torch.bfloat16
+            and out.dtype == torch.bfloat16 and (dim, vdim) in SIGMOID_MMA_DIMS and page_shift == 6
+            and q.stride(0) % 2 == 0 and out.stride(0) % 2 == 0 and q.data_ptr() % 4 == 0 and out.data_ptr() % 4 == 0
+            and k_cache.is_contiguous() and v_cache.is_contiguous() and k_cache.data_ptr() % 16 == 0
+            and v_cache.data_ptr() % 16 == 0)
+
+
+def sigmoid_attention_mma(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, cu_new: torch.Tensor,
+                          seq_start: torch.Tensor, seq_slot: torch.Tensor, page_table: torch.Tensor,
+                          bias: Optional[torch.Tensor], out: torch.Tensor, max_new: int, n_q: int, n_kv: int, dim: int,
+                          vdim: int, page_shift: int, chunk: Optional[int], window: Optional[int], scale: float,
+                          split: Optional[bool] = None, pdl: bool = False) -> None:
+    """``sigmoid_attention_plain`` on mma.sync for bfloat16: a block streams a sequence's pages once for a tile of
+    (token, head of one kv group) rows; weights float32, entering the second product as hi + lo bfloat16.
+    ``split`` (default: steps of one token a sequence): 16 rows a block, the warps share a page's keys."""
+    if not sigmoid_attention_mma_ok(q, k_cache, v_cache, out, dim, vdim, page_shift) or n_q % n_kv:
+        raise KernelError(f"sigmoid_attention_mma: dim {dim}, vdim {vdim}, heads {n_q}/{n_kv} or operands not supported")
+    _need(cu_new, "cu_new", torch.int32, 1); _need(seq_start, "seq_start", torch.int32, 1); _need(seq_slot, "seq_slot", torch.int32, 1)
+    _need(page_table, "page_table", torch.int32, 2)
+    B = seq_slot.shape[0]
+    if cu_new.shape[0] != B + 1 or seq_start.shape[0] != B or out.shape[0] != q.shape[0] or out.shape[1] < n_q * vdim \
+            or q.shape[1] < n_q * dim:
+        raise KernelError("sigmoid_attention_mma: shapes")
+    if bias is not None:
+        _need(bias, "bias", torch.float32, 1)
+        if bias.shape[0] != n_q:
+            raise KernelError("sigmoid_attention_mma: one bias per query head")
+    if split is None:
+        split = max_new * (n_q // n_kv) <= 16
+    _check(_fn("gated_attention", "ssb_sigmoid_attention_mma")(
+        _ptr(q), c_int(q.stride(0)), _ptr(k_cache), _ptr(v_cache), _ptr(cu_new), _ptr(seq_start), _ptr(seq_slot),
+        _ptr(page_table), c_int(page_table.shape[1]), _ptr(bias), _ptr(out), c_int(out.stride(0)), c_int(B),
+        c_int(max_new), c_int(n_q), c_int(n_kv), c_int(dim), c_int(vdim), c_int(page_shift),
+        c_int(int(chunk) if chunk else 0), c_int(int(window) if window else 0), c_float(scale), c_int(1 if split else 0),
+        c_int(1 if pdl else 0), _stream()), "sigmoid_attention_mma")
 
 
 def sigmoid_attention_plain(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, pos: torch.Tensor,

@@ -270,25 +270,22 @@ SSB_API int ssb_gated_linear_scan(const void* proj, int ld, int dtype, int q_off
 template <typename T, typename TW>
 __global__ void __launch_bounds__(128)
 head_norm_gate_kernel(const float* __restrict__ o, int ldo, const TW* __restrict__ w, int w_stride, float eps,
-                      const T* __restrict__ gate, int ldg, int gate_kind, T* __restrict__ y, int ldy, int vdim) {
-    __shared__ float red[128];
-    const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+                      const T* __restrict__ gate, int ldg, int gate_kind, T* __restrict__ y, int ldy, int vdim, int n_heads) {
+    // a warp per (token, head): its lanes walk the head's columns and meet in shuffles
+    const int t = blockIdx.x, h = blockIdx.y * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     ssb_pdl_launch_dependents();
     ssb_pdl_wait();
+    if (h >= n_heads) return;
     const float* src = o + (size_t)t * ldo + (size_t)h * vdim;
     float part = 0.f;
-    for (int c = tid; c < vdim; c += 128) part = fmaf(src[c], src[c], part);
-    red[tid] = part;
-    __syncthreads();
-    for (int s = 64; s > 0; s >>= 1) {
-        if (tid < s) red[tid] += red[tid + s];
-        __syncthreads();
-    }
-    const float inv = 1.0f / sqrtf(red[0] / (float)vdim + eps);
+    for (int c = lane; c < vdim; c += 32) part = fmaf(src[c], src[c], part);
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) part += __shfl_xor_sync(0xffffffffu, part, m);
+    const float inv = 1.0f / sqrtf(part / (float)vdim + eps);
     const T* gr = gate + (size_t)t * ldg + (size_t)h * vdim;
     const TW* wr = w + (size_t)h * w_stride;
     T* dst = y + (size_t)t * ldy + (size_t)h * vdim;
-    for (int c = tid; c < vdim; c += 128) {
+    for (int c = lane; c < vdim; c += 32) {
         const float gv = ssb_to_float(gr[c]);
         const float sg = 1.0f / (1.0f + expf(-gv));
         const float ga = gate_kind == 0 ? gv * sg : gate_kind == 1 ? sg : gv;
@@ -301,11 +298,11 @@ SSB_API int ssb_head_norm_gate(const float* o, int ldo, const void* w, int w_dty
                                int n_heads, int vdim, int pdl, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (vdim <= 0 || n_heads <= 0 || n_heads > 65535 || gate_kind < 0 || gate_kind > 2) return SSB_ERR_BAD_SIZE;
-    const dim3 grid(n_tokens, n_heads);
+    const dim3 grid(n_tokens, (n_heads + 3) / 4);
     int rc = 0;
 #define SSB_HNG(T, TW) \
     rc = ssb_launch(head_norm_gate_kernel<T, TW>, grid, dim3(128), 0, stream, pdl != 0, o, ldo, (const TW*)w, w_stride, eps, \
-                    (const T*)gate, ldg, gate_kind, (T*)y, ldy, vdim)
+                    (const T*)gate, ldg, gate_kind, (T*)y, ldy, vdim, n_heads)
     if (dtype == SSB_F32 && w_dtype == SSB_F32) SSB_HNG(float, float);
     else if (dtype == SSB_BF16 && w_dtype == SSB_BF16) SSB_HNG(bf16, bf16);
     else if (dtype == SSB_BF16 && w_dtype == SSB_F32) SSB_HNG(bf16, float);
@@ -330,23 +327,23 @@ constexpr int MS_COLS = 16;          // value columns a block of 128 threads own
 constexpr int MS_TOKENS = 4;         // tokens staged per pair of barriers
 constexpr int MS_THREADS = MS_LANES * MS_COLS;
 
-// Decays in place and, for the delta rule, unit keys and removal vectors.  One block per (token, head).
+// Decays in place and, for the delta rule, unit keys and removal vectors.  One warp per (token, head).
 //   decay_kind 0: z <- exp(-exp(z + z_bias));  1: z <- exp(-decay_scale * sigmoid(z + z_bias));
 //   log_decay: z gets the decay's logarithm instead (the float32 path's scan takes the exponential in double)
 //   with_unit: unit[t] = [u | a * u], u = k / sqrt(sum(k^2) + unit_eps), a = sigmoid(a_pre + a_bias)
 template <typename T>
-__global__ void __launch_bounds__(64)
+__global__ void __launch_bounds__(128)
 state_scan_prepare_kernel(float* __restrict__ z, int ldz, const float* __restrict__ z_bias, int decay_kind,
                           int log_decay, float decay_scale, const T* __restrict__ proj, int ld, int k_off, int a_off,
                           const float* __restrict__ a_bias, float unit_eps, float* __restrict__ unit, int ldu,
                           int n_heads, int dim) {
-    __shared__ float red[64];
     ssb_pdl_launch_dependents();
     ssb_pdl_wait();
     const size_t t = blockIdx.x;
-    const int h = blockIdx.y, tid = threadIdx.x;
+    const int h = blockIdx.y * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;     // a warp per (token, head)
+    if (h >= n_heads) return;
     float* zr = z + t * ldz + (size_t)h * dim;
-    for (int i = tid; i < dim; i += 64) {
+    for (int i = lane; i < dim; i += 32) {
         const float v = zr[i] + z_bias[h * dim + i];
         const float lw = decay_kind == 0 ? -expf(v) : -decay_scale / (1.0f + expf(-v));
         zr[i] = log_decay ? lw : expf(lw);
@@ -355,20 +352,16 @@ state_scan_prepare_kernel(float* __restrict__ z, int ldz, const float* __restric
     const T* kr = proj + t * ld + k_off + (size_t)h * dim;
     const T* ar = proj + t * ld + a_off + (size_t)h * dim;
     float part = 0.f;
-    for (int i = tid; i < dim; i += 64) {
+    for (int i = lane; i < dim; i += 32) {
         const float k = ssb_to_float(kr[i]);
         part = fmaf(k, k, part);
     }
-    red[tid] = part;
-    __syncthreads();
-    for (int s = 32; s > 0; s >>= 1) {
-        if (tid < s) red[tid] += red[tid + s];
-        __syncthreads();
-    }
-    const float inv = 1.0f / sqrtf(red[0] + unit_eps);
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) part += __shfl_xor_sync(0xffffffffu, part, m);
+    const float inv = 1.0f / sqrtf(part + unit_eps);
     float* ur = unit + t * ldu + (size_t)h * dim;
     float* aur = ur + (size_t)n_heads * dim;
-    for (int i = tid; i < dim; i += 64) {
+    for (int i = lane; i < dim; i += 32) {
         const float u = ssb_to_float(kr[i]) * inv;
         const float a = 1.0f / (1.0f + expf(-(ssb_to_float(ar[i]) + a_bias[h * dim + i])));
         ur[i] = u;
@@ -382,13 +375,13 @@ SSB_API int ssb_state_scan_prepare(float* z, int ldz, const float* z_bias, int d
                                    cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (n_heads <= 0 || n_heads > 65535 || dim <= 0 || decay_kind < 0 || decay_kind > 1) return SSB_ERR_BAD_SIZE;
-    const dim3 grid(n_tokens, n_heads);
+    const dim3 grid(n_tokens, (n_heads + 3) / 4);
     int rc;
     if (dtype == SSB_F32)
-        rc = ssb_launch(state_scan_prepare_kernel<float>, grid, dim3(64), 0, stream, pdl != 0, z, ldz, z_bias, decay_kind,
+        rc = ssb_launch(state_scan_prepare_kernel<float>, grid, dim3(128), 0, stream, pdl != 0, z, ldz, z_bias, decay_kind,
                         log_decay, decay_scale, (const float*)proj, ld, k_off, a_off, a_bias, unit_eps, unit, ldu, n_heads, dim);
     else if (dtype == SSB_BF16)
-        rc = ssb_launch(state_scan_prepare_kernel<bf16>, grid, dim3(64), 0, stream, pdl != 0, z, ldz, z_bias, decay_kind,
+        rc = ssb_launch(state_scan_prepare_kernel<bf16>, grid, dim3(128), 0, stream, pdl != 0, z, ldz, z_bias, decay_kind,
                         log_decay, decay_scale, (const bf16*)proj, ld, k_off, a_off, a_bias, unit_eps, unit, ldu, n_heads, dim);
     else
         return SSB_ERR_BAD_DTYPE;
@@ -539,6 +532,154 @@ matrix_state_scan_kernel(const T* __restrict__ proj, int ld, int r_off, int k_of
     }
 }
 
+// The same walk for bfloat16 projections whose rows can be fetched in 16-byte pieces: the vectors of four tokens
+// a stage go from global to shared memory by cp.async in the types they are stored in (decays and unit keys
+// float32, r, k and v bfloat16), four stages deep, so that the loads of the next twelve tokens are in flight
+// while four are worked on, with one barrier per four tokens.  (With the vectors staged through registers the
+// walk waited on global memory at every turn: four warps an SM hide nothing.)
+template <int RPL, bool DELTA>
+__global__ void __launch_bounds__(MS_THREADS)
+matrix_state_scan_async_kernel(const bf16* __restrict__ proj, int ld, int r_off, int k_off, int v_off,
+                               const float* __restrict__ decay, int ldd, const float* __restrict__ unit, int ldu,
+                               const float* __restrict__ bonus, float* __restrict__ state,
+                               const int* __restrict__ cu_new, const int* __restrict__ seq_slot,
+                               float* __restrict__ out, int ldo, int n_heads, int dim, int vdim) {
+    constexpr int DIMP = MS_LANES * RPL, STAGES = 4, TOK = MS_TOKENS;
+    constexpr int NF = DELTA ? 3 : 1;                    // float32 vectors a token: w (, u, a * u)
+    constexpr int F_BYTES = NF * TOK * DIMP * 4, KR_BYTES = 2 * TOK * DIMP * 2, V_BYTES = TOK * MS_COLS * 2;
+    constexpr int STAGE_BYTES = F_BYTES + KR_BYTES + V_BYTES;
+    extern __shared__ __align__(16) unsigned char ms_smem[];
+    const int b = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * MS_COLS;
+    const int tid = threadIdx.x, sub = tid % MS_LANES, cj = tid / MS_LANES;
+    ssb_pdl_launch_dependents();
+    ssb_pdl_wait();
+    const int slot = seq_slot[b];
+    if (slot < 0) return;
+    const int t0 = cu_new[b], t1 = cu_new[b + 1];
+    if (t0 >= t1) return;
+    const bool col = j0 + cj < vdim;
+    float* S = state + ((size_t)slot * n_heads + h) * dim * vdim;
+    float s_reg[RPL], b_reg[RPL];
+#pragma unroll
+    for (int r = 0; r < RPL; ++r) {
+        const int i = sub * RPL + r;
+        s_reg[r] = (col && i < dim) ? S[(size_t)i * vdim + j0 + cj] : 0.f;
+        b_reg[r] = (!DELTA && bonus != nullptr && i < dim) ? bonus[h * dim + i] : 0.f;
+    }
+    for (int e = tid; e < STAGES * STAGE_BYTES / 4; e += MS_THREADS) reinterpret_cast<uint32_t*>(ms_smem)[e] = 0u;
+    __syncthreads();                                     // rows past dim and columns past vdim stay zero
+    const int cf = dim / 4, cb = dim / 8, per_tok = NF * cf + 2 * cb + 2;
+    auto issue = [&](int t, int stage) {
+        const int n_tok = max(0, min(TOK, t1 - t));
+        unsigned char* base = ms_smem + stage * STAGE_BYTES;
+        for (int c = tid; c < n_tok * per_tok; c += MS_THREADS) {
+            const int tt = c / per_tok;
+            int e = c % per_tok;
+            const size_t row = (size_t)(t + tt);
+            const void* src;
+            unsigned char* dst;
+            if (e < NF * cf) {
+                const int vid = e / cf, ch = e % cf;
+                src = (vid == 0 ? decay + row * ldd : unit + row * ldu + (size_t)(vid - 1) * n_heads * dim) + h * dim + ch * 4;
+                dst = base + ((vid * TOK + tt) * DIMP + ch * 4) * 4;
+            } else if ((e -= NF * cf) < 2 * cb) {
+                const int which = e / cb, ch = e % cb;     // 0: k, 1: r
+                src = proj + row * ld + (which ? r_off : k_off) + h * dim + ch * 8;
+                dst = base + F_BYTES + ((which * TOK + tt) * DIMP + ch * 8) * 2;
+            } else {
+                e -= 2 * cb;
+                if (j0 + e * 8 >= vdim) continue;
+                src = proj + row * ld + v_off + h * vdim + j0 + e * 8;
+                dst = base + F_BYTES + KR_BYTES + (tt * MS_COLS + e * 8) * 2;
+            }
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+#pragma unroll
+    for (int st = 0; st < STAGES - 1; ++st) issue(t0 + st * TOK, st);
+    int it = 0;
+    for (int t = t0; t < t1; t += TOK, ++it) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");
+        __syncthreads();                                 // this stage has landed; everyone is done with the one before
+        issue(t + (STAGES - 1) * TOK, (it + STAGES - 1) % STAGES);
+        const unsigned char* base = ms_smem + (it % STAGES) * STAGE_BYTES;
+        const float* fv = reinterpret_cast<const float*>(base);
+        const bf16* kr = reinterpret_cast<const bf16*>(base + F_BYTES);
+        const bf16* vs = reinterpret_cast<const bf16*>(base + F_BYTES + KR_BYTES);
+        const int n_tok = min(TOK, t1 - t);
+        // the four tokens of a stage unrolled: the loads and conversions of a token overlap the chain of the one
+        // before, and the sums over a column's lanes for the outputs are taken for all four at the end
+        float o_part[TOK];
+#pragma unroll
+        for (int tt = 0; tt < TOK; ++tt) {
+            o_part[tt] = 0.f;
+            if (tt >= n_tok) continue;                   // only a sequence's last stage is short
+            const float v = __bfloat162float(vs[tt * MS_COLS + cj]);
+            const float* wv = fv + tt * DIMP + sub * RPL;
+            const __nv_bfloat162* k2 = reinterpret_cast<const __nv_bfloat162*>(kr + tt * DIMP + sub * RPL);
+            const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(kr + (TOK + tt) * DIMP + sub * RPL);
+            float o0 = 0.f, o1 = 0.f;
+            if (DELTA) {
+                const float* uv = fv + (TOK + tt) * DIMP + sub * RPL;
+                const float* auv = fv + (2 * TOK + tt) * DIMP + sub * RPL;
+                float seen0 = 0.f, seen1 = 0.f;
+#pragma unroll
+                for (int r = 0; r < RPL; r += 4) {
+                    const float4 u = *reinterpret_cast<const float4*>(uv + r);
+                    seen0 = fmaf(u.x, s_reg[r], seen0);
+                    seen1 = fmaf(u.y, s_reg[r + 1], seen1);
+                    seen0 = fmaf(u.z, s_reg[r + 2], seen0);
+                    seen1 = fmaf(u.w, s_reg[r + 3], seen1);
+                }
+                float seen = seen0 + seen1;
+                seen += __shfl_xor_sync(0xffffffffu, seen, 1);
+                seen += __shfl_xor_sync(0xffffffffu, seen, 2);
+                seen += __shfl_xor_sync(0xffffffffu, seen, 4);
+#pragma unroll
+                for (int r = 0; r < RPL; r += 4) {
+                    const float4 w = *reinterpret_cast<const float4*>(wv + r), au = *reinterpret_cast<const float4*>(auv + r);
+                    const float2 ka = __bfloat1622float2(k2[r / 2]), kb = __bfloat1622float2(k2[r / 2 + 1]);
+                    const float2 qa = __bfloat1622float2(r2[r / 2]), qb = __bfloat1622float2(r2[r / 2 + 1]);
+                    s_reg[r] = fmaf(w.x, s_reg[r], fmaf(ka.x, v, -au.x * seen));          o0 = fmaf(s_reg[r], qa.x, o0);
+                    s_reg[r + 1] = fmaf(w.y, s_reg[r + 1], fmaf(ka.y, v, -au.y * seen));  o1 = fmaf(s_reg[r + 1], qa.y, o1);
+                    s_reg[r + 2] = fmaf(w.z, s_reg[r + 2], fmaf(kb.x, v, -au.z * seen));  o0 = fmaf(s_reg[r + 2], qb.x, o0);
+                    s_reg[r + 3] = fmaf(w.w, s_reg[r + 3], fmaf(kb.y, v, -au.w * seen));  o1 = fmaf(s_reg[r + 3], qb.y, o1);
+                }
+            } else {
+#pragma unroll
+                for (int r = 0; r < RPL; r += 4) {
+                    const float4 w = *reinterpret_cast<const float4*>(wv + r);
+                    const float2 ka = __bfloat1622float2(k2[r / 2]), kb = __bfloat1622float2(k2[r / 2 + 1]);
+                    const float2 qa = __bfloat1622float2(r2[r / 2]), qb = __bfloat1622float2(r2[r / 2 + 1]);
+                    const float kv0 = ka.x * v, kv1 = ka.y * v, kv2 = kb.x * v, kv3 = kb.y * v;
+                    o0 = fmaf(fmaf(b_reg[r], kv0, s_reg[r]), qa.x, o0);          s_reg[r] = fmaf(w.x, s_reg[r], kv0);
+                    o1 = fmaf(fmaf(b_reg[r + 1], kv1, s_reg[r + 1]), qa.y, o1);  s_reg[r + 1] = fmaf(w.y, s_reg[r + 1], kv1);
+                    o0 = fmaf(fmaf(b_reg[r + 2], kv2, s_reg[r + 2]), qb.x, o0);  s_reg[r + 2] = fmaf(w.z, s_reg[r + 2], kv2);
+                    o1 = fmaf(fmaf(b_reg[r + 3], kv3, s_reg[r + 3]), qb.y, o1);  s_reg[r + 3] = fmaf(w.w, s_reg[r + 3], kv3);
+                }
+            }
+            o_part[tt] = o0 + o1;
+        }
+#pragma unroll
+        for (int tt = 0; tt < TOK; ++tt) o_part[tt] += __shfl_xor_sync(0xffffffffu, o_part[tt], 1);
+#pragma unroll
+        for (int tt = 0; tt < TOK; ++tt) o_part[tt] += __shfl_xor_sync(0xffffffffu, o_part[tt], 2);
+#pragma unroll
+        for (int tt = 0; tt < TOK; ++tt) o_part[tt] += __shfl_xor_sync(0xffffffffu, o_part[tt], 4);
+        if (sub == 0 && col)
+#pragma unroll
+            for (int tt = 0; tt < TOK; ++tt)
+                if (tt < n_tok) out[(size_t)(t + tt) * ldo + h * vdim + j0 + cj] = o_part[tt];
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+#pragma unroll
+    for (int r = 0; r < RPL; ++r) {
+        const int i = sub * RPL + r;
+        if (col && i < dim) S[(size_t)i * vdim + j0 + cj] = s_reg[r];
+    }
+}
+
 // proj [T, ld]: r, k (n_heads x dim) and v (n_heads x vdim) from the given columns; decay [T, ldd] float32
 // (n_heads x dim), for float32 rows their logarithms (what the prepare kernel leaves in either case); kind 0 (delta rule): unit [T, ldu] float32 = [u | a * u]; kind 1: bonus [n_heads x dim]
 // float32 or null; state [slots, n_heads, dim, vdim] float32; out [T, ldo] float32 (n_heads x vdim).
@@ -552,6 +693,31 @@ SSB_API int ssb_matrix_state_scan(const void* proj, int ld, int dtype, int r_off
     const dim3 grid(n_seqs, n_heads, (vdim + MS_COLS - 1) / MS_COLS);
     if (grid.y > 65535 || grid.z > 65535) return SSB_ERR_BAD_SIZE;
     int rc = 0;
+    // bfloat16 rows whose pieces of 16 bytes are aligned take the cp.async form
+    const bool pieces = dtype == SSB_BF16 && dim % 8 == 0 && dim <= 128 && vdim % 8 == 0 && ld % 8 == 0 && r_off % 8 == 0 &&
+                        k_off % 8 == 0 && v_off % 8 == 0 && ldd % 4 == 0 && (kind != 0 || ldu % 4 == 0) &&
+                        !(((uintptr_t)proj | (uintptr_t)decay | (uintptr_t)unit) & 15);
+    if (pieces) {
+#define SSB_MSA(RPL, DELTA) do { \
+        constexpr int stage = ((DELTA ? 3 : 1) * MS_TOKENS * MS_LANES * RPL * 4) + 2 * MS_TOKENS * MS_LANES * RPL * 2 + MS_TOKENS * MS_COLS * 2; \
+        auto kern = matrix_state_scan_async_kernel<RPL, DELTA>; \
+        if (4 * stage > 48 * 1024) { \
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * stage); \
+            if (e != cudaSuccess) return (int)e; \
+        } \
+        rc = ssb_launch(kern, grid, dim3(MS_THREADS), (size_t)4 * stage, stream, pdl != 0, (const bf16*)proj, ld, r_off, k_off, v_off, \
+                        decay, ldd, unit, ldu, bonus, state, cu_new, seq_slot, out, ldo, n_heads, dim, vdim); \
+    } while (0)
+#define SSB_MSA_DIM(DELTA) do { \
+        if (dim <= 32) SSB_MSA(4, DELTA); \
+        else if (dim <= 64) SSB_MSA(8, DELTA); \
+        else SSB_MSA(16, DELTA); \
+    } while (0)
+        if (kind == 0) SSB_MSA_DIM(true); else SSB_MSA_DIM(false);
+#undef SSB_MSA_DIM
+#undef SSB_MSA
+        return rc ? rc : ssb_launch_status();
+    }
 #define SSB_MS(T, RPL, DELTA) \
     rc = ssb_launch(matrix_state_scan_kernel<T, RPL, DELTA>, grid, dim3(MS_THREADS), 0, stream, pdl != 0, (const T*)proj, ld, \
                     r_off, k_off, v_off, decay, ldd, unit, ldu, bonus, state, cu_new, seq_slot, out, ldo, n_heads, dim, vdim)
@@ -637,6 +803,87 @@ gated_unit_scan_kernel(const float* __restrict__ gates, int ldg, const float* __
             }
     }
     state[(size_t)slot * channels + c] = (float)S;
+}
+
+// The same recurrence in two launches, for long runs of new tokens in the 16-bit path: everything that does not
+// depend on the state (the two gates, a, the input's share) is taken for all tokens at once, a and the share
+// written over g_r and g_i; the walk over the tokens is then one multiply-add a token.
+__global__ void __launch_bounds__(256)
+gated_unit_prepare_kernel(float* __restrict__ gates, int ldg, const float* __restrict__ bias_r,
+                          const float* __restrict__ bias_i, const float* __restrict__ rate, const bf16* __restrict__ u,
+                          int ldu, int channels, int block, size_t total) {
+    ssb_pdl_launch_dependents();
+    ssb_pdl_wait();
+    const size_t idx = (size_t)blockIdx.x * 256 + threadIdx.x;
+    if (idx >= total) return;
+    const size_t row = idx / channels;
+    const int c = (int)(idx % channels);
+    const int gc = (c / block) * 2 * block + c % block;
+    float* g = gates + row * ldg + gc;
+    const float r = 1.0f / (1.0f + expf(-(g[0] + bias_r[c])));
+    const float i = 1.0f / (1.0f + expf(-(g[block] + bias_i[c])));
+    const float log_a = rate[c] * r;
+    g[0] = expf(log_a);
+    g[block] = sqrtf(-expm1f(2.0f * log_a)) * i * __bfloat162float(u[row * ldu + c]);
+}
+
+__global__ void __launch_bounds__(64)
+gated_unit_walk_kernel(const float* __restrict__ gates, int ldg, const bf16* __restrict__ y, int ldy,
+                       const float* __restrict__ y_bias, float* __restrict__ state, const int* __restrict__ cu_new,
+                       const int* __restrict__ seq_slot, bf16* __restrict__ out, int ldo, int channels, int block) {
+    constexpr int AHEAD = 8;
+    ssb_pdl_launch_dependents();
+    ssb_pdl_wait();
+    const int b = blockIdx.x, c = blockIdx.y * 64 + threadIdx.x;
+    const int slot = seq_slot[b];
+    if (slot < 0 || c >= channels) return;
+    const int t0 = cu_new[b], t1 = cu_new[b + 1];
+    const int gc = (c / block) * 2 * block + c % block;
+    const float yb = y_bias ? y_bias[c] : 0.f;
+    float S = state[(size_t)slot * channels + c];
+    float a[AHEAD], sh[AHEAD], yy[AHEAD];
+    auto fetch = [&](int t) {
+#pragma unroll
+        for (int n = 0; n < AHEAD; ++n)
+            if (t + n < t1) {
+                const size_t row = (size_t)(t + n);
+                a[n] = gates[row * ldg + gc];
+                sh[n] = gates[row * ldg + gc + block];
+                yy[n] = __bfloat162float(y[row * ldy + c]);
+            }
+    };
+    fetch(t0);
+    for (int t = t0; t < t1; t += AHEAD) {
+        float ca[AHEAD], cs[AHEAD], cy[AHEAD];
+#pragma unroll
+        for (int n = 0; n < AHEAD; ++n) { ca[n] = a[n]; cs[n] = sh[n]; cy[n] = yy[n]; }
+        if (t + AHEAD < t1) fetch(t + AHEAD);
+#pragma unroll
+        for (int n = 0; n < AHEAD; ++n)
+            if (t + n < t1) {
+                S = fmaf(ca[n], S, cs[n]);
+                out[(size_t)(t + n) * ldo + c] = __float2bfloat16_rn(S * gelu_tanh_f(cy[n] + yb));
+            }
+    }
+    state[(size_t)slot * channels + c] = S;
+}
+
+SSB_API int ssb_gated_unit_scan_split(float* gates, int ldg, const float* bias_r, const float* bias_i, const float* rate,
+                                      const void* u, int ldu, const void* y, int ldy, const float* y_bias, float* state,
+                                      const int* cu_new, const int* seq_slot, void* out, int ldo, int n_seqs, int n_tokens,
+                                      int channels, int block, int pdl, cudaStream_t stream) {
+    if (n_seqs <= 0 || n_tokens <= 0) return 0;
+    if (channels <= 0 || block <= 0 || channels % block) return SSB_ERR_BAD_SIZE;
+    const size_t total = (size_t)n_tokens * channels;
+    int rc = ssb_launch(gated_unit_prepare_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, pdl != 0, gates,
+                        ldg, bias_r, bias_i, rate, (const bf16*)u, ldu, channels, block, total);
+    if (!rc) rc = ssb_launch_status();
+    if (rc) return rc;
+    const dim3 grid(n_seqs, (channels + 63) / 64);
+    if (grid.y > 65535) return SSB_ERR_BAD_SIZE;
+    rc = ssb_launch(gated_unit_walk_kernel, grid, dim3(64), 0, stream, pdl != 0, (const float*)gates, ldg, (const bf16*)y, ldy,
+                    y_bias, state, cu_new, seq_slot, (bf16*)out, ldo, channels, block);
+    return rc ? rc : ssb_launch_status();
 }
 
 SSB_API int ssb_gated_unit_scan(const float* gates, int ldg, const float* bias_r, const float* bias_i, const float* rate,

@@ -124,7 +124,7 @@ shift_mix_kernel(const T* __restrict__ h, int ldh, const float* __restrict__ mu,
     const int t0 = cu_new[b], t1 = cu_new[b + 1];
     const int lo = t0 + blockIdx.y * tile, hi = min(t1, lo + tile);
     if (lo >= hi) return;
-    for (int c = tid; c < width; c += SEQ_THREADS) {
+    for (int c = blockIdx.z * SEQ_THREADS + tid; c < width; c += gridDim.z * SEQ_THREADS) {
         float before;
         if (lo == t0) {
             float* keep = last + (size_t)slot * width + c;
@@ -148,7 +148,7 @@ SSB_API int ssb_shift_mix(const void* h, int ldh, int dtype, const float* mu, in
     if (n_seqs <= 0 || max_new <= 0) return 0;
     if (width <= 0 || n_mix <= 0) return SSB_ERR_BAD_SIZE;
     const int tile = 8;
-    const dim3 grid(n_seqs, (max_new + tile - 1) / tile);
+    const dim3 grid(n_seqs, (max_new + tile - 1) / tile, min((width + SEQ_THREADS - 1) / SEQ_THREADS, 64));
     if (grid.y > 65535) return SSB_ERR_BAD_SIZE;
     int rc;
     if (dtype == SSB_F32)

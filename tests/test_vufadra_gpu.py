@@ -178,6 +178,41 @@ def test_mixer_pair_alone(dtype):
     assert float((got - ref).abs().max()) < tolerance(dtype, ref)
 
 
+@pytest.mark.parametrize("dim,vdim,heads,kv_heads,chunk", [(64, 64, 8, 2, 128), (96, 64, 6, 6, 20), (128, 128, 4, 1, 70),
+                                                            (64, 128, 16, 1, 64), (96, 96, 2, 1, 33), (128, 64, 3, 3, 200)])
+def test_sigmoid_attention_kernels_agree(dim, vdim, heads, kv_heads, chunk):
+    """The tensor-core kernel against the plain one in bfloat16, for every pair of head sizes it takes: three
+    sequences of unequal lengths as prompts that continue a cache, and as decode steps, with pages in a shuffled
+    order; the two differ by the rounding of the output alone."""
+    from supersonic_b200.csrc import ops
+    g = torch.Generator(device=DEV).manual_seed(dim + vdim)
+    lens, new = [300, 64, 131], [170, 64, 1]
+    pages_per, B = 6, 3
+    kc = (torch.randn(B * pages_per + 1, kv_heads, 64, dim, device=DEV, generator=g) * 0.6).bfloat16()
+    vc = (torch.randn(B * pages_per + 1, kv_heads, 64, vdim, device=DEV, generator=g) * 0.6).bfloat16()
+    table = (torch.randperm(B * pages_per, device=DEV, generator=g).int() + 1).view(B, pages_per).contiguous()
+    bias = torch.randn(heads, device=DEV, generator=g) - 1.0
+    for counts in (new, [1, 1, 1]):
+        T = sum(counts)
+        q = (torch.randn(T, heads * dim + 8, device=DEV, generator=g) * 0.6).bfloat16()[:, :heads * dim]
+        pos = torch.cat([torch.arange(n - c, n) for n, c in zip(lens, counts)]).int().to(DEV)
+        slot = torch.cat([torch.full((c,), i) for i, c in enumerate(counts)]).int().to(DEV)
+        cu = torch.tensor([0] + list(np.cumsum(counts)), dtype=torch.int32, device=DEV)
+        start = torch.tensor([n - c for n, c in zip(lens, counts)], dtype=torch.int32, device=DEV)
+        seq_slot = torch.arange(B, dtype=torch.int32, device=DEV)
+        want = torch.empty(T, heads * vdim, device=DEV, dtype=torch.bfloat16)
+        ops.sigmoid_attention_plain(q, kc, vc, pos, slot, table, bias, want, heads, kv_heads, dim, vdim, 6, chunk, None, dim ** -0.5)
+        for window in (None, 45):
+            if window:
+                ops.sigmoid_attention_plain(q, kc, vc, pos, slot, table, bias, want, heads, kv_heads, dim, vdim, 6, chunk, window, dim ** -0.5)
+            for split in (None, True, False):
+                got = torch.zeros_like(want)
+                ops.sigmoid_attention_mma(q, kc, vc, cu, start, seq_slot, table, bias, got, max(counts), heads, kv_heads, dim, vdim,
+                                          6, chunk, window, dim ** -0.5, split=split)
+                err = float((got.float() - want.float()).abs().max())
+                assert err < 0.02 * max(1.0, float(want.float().abs().max())), (counts, window, split, err)
+
+
 def test_pair_embedding_and_token_shift_in_a_batch_of_portions():
     """Three sequences whose tokens arrive in unequal portions, several sequences a step: the row picked by the
     token before (the table's last row for a sequence's first token) and the mix with the row before, across
