@@ -259,7 +259,9 @@ def gated_unit_scan(args):
     cu = torch.arange(0, (B + 1) * T, T, dtype=torch.int32, device=DEV)
     slots = torch.arange(1, B + 1, dtype=torch.int32, device=DEV)
     out = torch.empty(B * T, C, device=DEV, dtype=torch.bfloat16)
-    us = _time(lambda i: ops.gated_unit_scan(gates, br, bi, rate, u, y, yb, state, cu, slots, out, bs, max_new=T), args.iters)
+    scratch = torch.empty(ops.gated_unit_scan_scratch(B, T, C), device=DEV)
+    us = _time(lambda i: ops.gated_unit_scan(gates, br, bi, rate, u, y, yb, state, cu, slots, out, bs, max_new=T,
+                                             scratch=scratch), args.iters)
     return {"kernel": "gated_unit_scan", "seqs": B, "tokens": T, "channels": C, "us": round(us, 2),
             "GB/s": round(B * T * C * 14 / us / 1e3, 1)}
 

@@ -355,6 +355,9 @@ class FastKernels(PlainKernels):
                                  page_table, out, sinks, batch.max_new, n_heads, dk, kv_rank, page_shift, window,
                                  scale, splits, partial, pdl=self.pdl)
 
+    def _scan_scratch(self, n, device):
+        return self._buffer("unit_scan_chunks", n, torch.float32, device)
+
     def sigmoid_attention(self, q, k_cache, v_cache, batch, page_table, bias, out, n_q, n_kv, dim, vdim, page_shift,
                           chunk, window, scale):
         if ops.sigmoid_attention_mma_ok(q, k_cache, v_cache, out, dim, vdim, page_shift):

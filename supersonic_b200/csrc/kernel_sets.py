@@ -158,9 +158,15 @@ class PlainKernels:
         ops.matrix_state_scan(proj, r_off, k_off, v_off, decay, kind, state, batch.cu_new, batch.seq_slot, out,
                               n_heads, dim, vdim, unit=unit, bonus=bonus, pdl=self._chain(batch.n_tokens))
 
+    def _scan_scratch(self, n, device):
+        return torch.empty(n, dtype=torch.float32, device=device)
+
     def gated_unit_scan(self, gates, bias_r, bias_i, rate, u, y, y_bias, state, batch, out, block):
+        scratch = None
+        if u.dtype == torch.bfloat16 and batch.max_new >= ops.GATED_UNIT_SPLIT_MIN_NEW:       # a long run: chunks in parallel
+            scratch = self._scan_scratch(ops.gated_unit_scan_scratch(batch.n_seqs, batch.max_new, state.shape[1]), out.device)
         ops.gated_unit_scan(gates, bias_r, bias_i, rate, u, y, y_bias, state, batch.cu_new, batch.seq_slot, out, block,
-                            max_new=batch.max_new, pdl=self._chain(batch.n_tokens))
+                            max_new=batch.max_new, scratch=scratch, pdl=self._chain(batch.n_tokens))
 
     # ---- along a sequence --------------------------------------------------------------
     def pair_embed(self, ids, table, pair, prev, batch, out, buckets, mul_prev, mul_cur):

@@ -542,18 +542,26 @@ def matrix_state_scan(proj: torch.Tensor, r_off: int, k_off: int, v_off: int, de
         _stream()), "matrix_state_scan")
 
 
-GATED_UNIT_SPLIT_MIN_NEW = 16    # runs of new tokens from which the vector-state recurrence takes its two-launch form
+GATED_UNIT_SPLIT_MIN_NEW = 64    # runs of new tokens from which the vector-state recurrence takes its chunked form
+GATED_UNIT_CHUNK = 128
+
+
+def gated_unit_scan_scratch(n_seqs: int, max_new: int, channels: int) -> int:
+    """float32 elements of scratch the chunked walk needs: (A, B) per sequence, chunk and channel."""
+    return 2 * n_seqs * (-(-max_new // GATED_UNIT_CHUNK)) * channels
 
 
 def gated_unit_scan(gates: torch.Tensor, bias_r: torch.Tensor, bias_i: torch.Tensor, rate: torch.Tensor,
                     u: torch.Tensor, y: torch.Tensor, y_bias: Optional[torch.Tensor], state: torch.Tensor,
                     cu_new: torch.Tensor, seq_slot: torch.Tensor, out: torch.Tensor, block: int,
-                    max_new: int = 1, pdl: bool = False) -> None:
+                    max_new: int = 1, scratch: Optional[torch.Tensor] = None, pdl: bool = False) -> None:
     """Per sequence and channel over the new tokens: r = sigmoid(g_r + bias_r), i = sigmoid(g_i + bias_i),
     a = exp(rate * r), S = a S + sqrt(1 - a^2) i u, out = S * gelu_tanh(y + y_bias).  ``gates`` [T, 2 x channels]
     float32 holds [g_r | g_i] per block of ``block`` channels; S float32 lives in ``state[slot]``.  Runs of
-    ``GATED_UNIT_SPLIT_MIN_NEW`` and more new tokens in bfloat16 take two launches: what does not depend on the state
-    for all tokens at once (written over ``gates``), then a walk of one multiply-add a token."""
+    ``GATED_UNIT_SPLIT_MIN_NEW`` and more new tokens in bfloat16, given ``scratch`` (float32,
+    ``gated_unit_scan_scratch`` elements), take several launches: what does not depend on the state for all tokens at
+    once (written over ``gates``, and the activation of ``y`` over ``y``), then the walk over chunks of 128 tokens in
+    parallel (each chunk from zero, the chunks' ends in order, each chunk from its true start)."""
     _need(gates, "gates", torch.float32, 2); _need(u, "u", None, 2); _need(y, "y", u.dtype, 2); _need(out, "out", u.dtype, 2)
     _need(state, "state", torch.float32, 2)
     C = state.shape[1]
@@ -565,12 +573,15 @@ def gated_unit_scan(gates: torch.Tensor, bias_r: torch.Tensor, bias_i: torch.Ten
     if gates.shape[0] != T or gates.shape[1] < 2 * C or min(u.shape[1], y.shape[1], out.shape[1]) < C or y.shape[0] != T \
             or out.shape[0] != T or cu_new.shape[0] != B + 1 or C % block or not state.is_contiguous():
         raise KernelError("gated_unit_scan: sizes")
-    if u.dtype == torch.bfloat16 and max_new >= GATED_UNIT_SPLIT_MIN_NEW:
+    if u.dtype == torch.bfloat16 and max_new >= GATED_UNIT_SPLIT_MIN_NEW and scratch is not None:
+        _need(scratch, "scratch", torch.float32)
+        if scratch.numel() < gated_unit_scan_scratch(B, max_new, C):
+            raise KernelError("gated_unit_scan: the scratch of the chunked walk is too small")
         _check(_fn("recurrence_ops", "ssb_gated_unit_scan_split")(
             _ptr(gates), c_int(gates.stride(0)), _ptr(bias_r), _ptr(bias_i), _ptr(rate), _ptr(u), c_int(u.stride(0)),
             _ptr(y), c_int(y.stride(0)), _ptr(y_bias), _ptr(state), _ptr(cu_new), _ptr(seq_slot), _ptr(out),
-            c_int(out.stride(0)), c_int(B), c_int(T), c_int(C), c_int(block), c_int(1 if pdl else 0), _stream()),
-            "gated_unit_scan_split")
+            c_int(out.stride(0)), c_int(B), c_int(T), c_int(max_new), c_int(C), c_int(block), _ptr(scratch),
+            c_int(1 if pdl else 0), _stream()), "gated_unit_scan_split")
         return
     _check(_fn("recurrence_ops", "ssb_gated_unit_scan")(
         _ptr(gates), c_int(gates.stride(0)), _ptr(bias_r), _ptr(bias_i), _ptr(rate), _ptr(u), c_int(u.stride(0)),

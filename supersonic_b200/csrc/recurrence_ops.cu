@@ -568,32 +568,53 @@ matrix_state_scan_async_kernel(const bf16* __restrict__ proj, int ld, int r_off,
     }
     for (int e = tid; e < STAGES * STAGE_BYTES / 4; e += MS_THREADS) reinterpret_cast<uint32_t*>(ms_smem)[e] = 0u;
     __syncthreads();                                     // rows past dim and columns past vdim stay zero
+    // the 16-byte pieces of a stage are the same in every stage but for the token they start from: each thread
+    // works out its pieces once (where in a row, which array, where in the stage) and only adds the row offset
+    constexpr int NCH = (TOK * (NF * (DIMP / 4) + 2 * (DIMP / 8) + 2) + MS_THREADS - 1) / MS_THREADS;
     const int cf = dim / 4, cb = dim / 8, per_tok = NF * cf + 2 * cb + 2;
+    const unsigned char* c_src[NCH];
+    long long c_step[NCH];                               // bytes from a row to the next in the piece's array
+    int c_dst[NCH], c_tt[NCH];                           // c_tt = TOK: no piece
+#pragma unroll
+    for (int n = 0; n < NCH; ++n) {
+        const int c = n * MS_THREADS + tid;
+        c_tt[n] = TOK;
+        c_src[n] = nullptr;
+        c_step[n] = 0;
+        c_dst[n] = 0;
+        if (c >= TOK * per_tok) continue;
+        const int tt = c / per_tok;
+        int e = c % per_tok;
+        if (e < NF * cf) {
+            const int vid = e / cf, ch = e % cf;
+            const float* base = vid == 0 ? decay : unit + (size_t)(vid - 1) * n_heads * dim;
+            c_step[n] = (long long)(vid == 0 ? ldd : ldu) * 4;
+            c_src[n] = reinterpret_cast<const unsigned char*>(base + h * dim + ch * 4) + (size_t)(t0 + tt) * c_step[n];
+            c_dst[n] = ((vid * TOK + tt) * DIMP + ch * 4) * 4;
+        } else if ((e -= NF * cf) < 2 * cb) {
+            const int which = e / cb, ch = e % cb;       // 0: k, 1: r
+            c_step[n] = (long long)ld * 2;
+            c_src[n] = reinterpret_cast<const unsigned char*>(proj + (which ? r_off : k_off) + h * dim + ch * 8) +
+                       (size_t)(t0 + tt) * c_step[n];
+            c_dst[n] = F_BYTES + ((which * TOK + tt) * DIMP + ch * 8) * 2;
+        } else {
+            e -= 2 * cb;
+            if (j0 + e * 8 >= vdim) continue;
+            c_step[n] = (long long)ld * 2;
+            c_src[n] = reinterpret_cast<const unsigned char*>(proj + v_off + h * vdim + j0 + e * 8) + (size_t)(t0 + tt) * c_step[n];
+            c_dst[n] = F_BYTES + KR_BYTES + (tt * MS_COLS + e * 8) * 2;
+        }
+        c_tt[n] = tt;
+    }
+    const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(ms_smem);
     auto issue = [&](int t, int stage) {
         const int n_tok = max(0, min(TOK, t1 - t));
-        unsigned char* base = ms_smem + stage * STAGE_BYTES;
-        for (int c = tid; c < n_tok * per_tok; c += MS_THREADS) {
-            const int tt = c / per_tok;
-            int e = c % per_tok;
-            const size_t row = (size_t)(t + tt);
-            const void* src;
-            unsigned char* dst;
-            if (e < NF * cf) {
-                const int vid = e / cf, ch = e % cf;
-                src = (vid == 0 ? decay + row * ldd : unit + row * ldu + (size_t)(vid - 1) * n_heads * dim) + h * dim + ch * 4;
-                dst = base + ((vid * TOK + tt) * DIMP + ch * 4) * 4;
-            } else if ((e -= NF * cf) < 2 * cb) {
-                const int which = e / cb, ch = e % cb;     // 0: k, 1: r
-                src = proj + row * ld + (which ? r_off : k_off) + h * dim + ch * 8;
-                dst = base + F_BYTES + ((which * TOK + tt) * DIMP + ch * 8) * 2;
-            } else {
-                e -= 2 * cb;
-                if (j0 + e * 8 >= vdim) continue;
-                src = proj + row * ld + v_off + h * vdim + j0 + e * 8;
-                dst = base + F_BYTES + KR_BYTES + (tt * MS_COLS + e * 8) * 2;
-            }
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
-        }
+        const long long rows = t - t0;
+#pragma unroll
+        for (int n = 0; n < NCH; ++n)
+            if (c_tt[n] < n_tok)
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_base + stage * STAGE_BYTES + c_dst[n]),
+                             "l"(c_src[n] + rows * c_step[n]) : "memory");
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
 #pragma unroll
@@ -805,13 +826,15 @@ gated_unit_scan_kernel(const float* __restrict__ gates, int ldg, const float* __
     state[(size_t)slot * channels + c] = (float)S;
 }
 
-// The same recurrence in two launches, for long runs of new tokens in the 16-bit path: everything that does not
-// depend on the state (the two gates, a, the input's share) is taken for all tokens at once, a and the share
-// written over g_r and g_i; the walk over the tokens is then one multiply-add a token.
+// The same recurrence in several launches, for long runs of new tokens in the 16-bit path: everything that does not
+// depend on the state (the two gates, a, the input's share, the activation of y) is taken for all tokens at once,
+// a and the share written over g_r and g_i and gelu_tanh(y + y_bias) over y; the walk over the tokens is then one
+// multiply-add and one product a token.
 __global__ void __launch_bounds__(256)
 gated_unit_prepare_kernel(float* __restrict__ gates, int ldg, const float* __restrict__ bias_r,
                           const float* __restrict__ bias_i, const float* __restrict__ rate, const bf16* __restrict__ u,
-                          int ldu, int channels, int block, size_t total) {
+                          int ldu, bf16* __restrict__ y, int ldy, const float* __restrict__ y_bias, int channels, int block,
+                          size_t total) {
     ssb_pdl_launch_dependents();
     ssb_pdl_wait();
     const size_t idx = (size_t)blockIdx.x * 256 + threadIdx.x;
@@ -825,22 +848,45 @@ gated_unit_prepare_kernel(float* __restrict__ gates, int ldg, const float* __res
     const float log_a = rate[c] * r;
     g[0] = expf(log_a);
     g[block] = sqrtf(-expm1f(2.0f * log_a)) * i * __bfloat162float(u[row * ldu + c]);
+    bf16* yp = y + row * ldy + c;
+    *yp = __float2bfloat16_rn(gelu_tanh_f(__bfloat162float(*yp) + (y_bias ? y_bias[c] : 0.f)));
 }
 
+// The walk itself, over chunks of a sequence's tokens in parallel (S_t = a_t S_(t-1) + s_t composes: a chunk is
+// S_out = A S_in + B with A the product of its a and B its own walk from zero).
+//   PHASE 0: every (sequence, chunk, channel) walks its chunk from zero and leaves (A, B) in scratch;
+//   PHASE 1: every (sequence, channel) walks the chunks in order from the slot's state, leaves each chunk's S_in in
+//            scratch and the last S_out in the state;
+//   PHASE 2: every (sequence, chunk, channel) walks its chunk from S_in and writes the outputs S_t * y_t.
+template <int PHASE>
 __global__ void __launch_bounds__(64)
 gated_unit_walk_kernel(const float* __restrict__ gates, int ldg, const bf16* __restrict__ y, int ldy,
-                       const float* __restrict__ y_bias, float* __restrict__ state, const int* __restrict__ cu_new,
-                       const int* __restrict__ seq_slot, bf16* __restrict__ out, int ldo, int channels, int block) {
+                       float* __restrict__ state, const int* __restrict__ cu_new, const int* __restrict__ seq_slot,
+                       bf16* __restrict__ out, int ldo, int channels, int block, int chunk, int max_chunks,
+                       float2* __restrict__ scratch) {
     constexpr int AHEAD = 8;
     ssb_pdl_launch_dependents();
     ssb_pdl_wait();
-    const int b = blockIdx.x, c = blockIdx.y * 64 + threadIdx.x;
+    const int b = blockIdx.x, c = blockIdx.y * 64 + threadIdx.x, ck = blockIdx.z;
     const int slot = seq_slot[b];
     if (slot < 0 || c >= channels) return;
-    const int t0 = cu_new[b], t1 = cu_new[b + 1];
+    const int s0 = cu_new[b], s1 = cu_new[b + 1];
+    float2* mine = scratch + ((size_t)b * max_chunks) * channels + c;      // [chunk][channel]
+    if (PHASE == 1) {
+        const int n = (s1 - s0 + chunk - 1) / chunk;
+        float S = state[(size_t)slot * channels + c];
+        for (int k = 0; k < n; ++k) {
+            const float2 ab = mine[(size_t)k * channels];
+            mine[(size_t)k * channels].x = S;
+            S = fmaf(ab.x, S, ab.y);
+        }
+        state[(size_t)slot * channels + c] = S;
+        return;
+    }
+    const int t0 = s0 + ck * chunk, t1 = min(s1, t0 + chunk);
+    if (t0 >= t1) return;
     const int gc = (c / block) * 2 * block + c % block;
-    const float yb = y_bias ? y_bias[c] : 0.f;
-    float S = state[(size_t)slot * channels + c];
+    float S = PHASE == 2 ? mine[(size_t)ck * channels].x : 0.f, A = 1.f;
     float a[AHEAD], sh[AHEAD], yy[AHEAD];
     auto fetch = [&](int t) {
 #pragma unroll
@@ -849,41 +895,55 @@ gated_unit_walk_kernel(const float* __restrict__ gates, int ldg, const bf16* __r
                 const size_t row = (size_t)(t + n);
                 a[n] = gates[row * ldg + gc];
                 sh[n] = gates[row * ldg + gc + block];
-                yy[n] = __bfloat162float(y[row * ldy + c]);
+                if (PHASE == 2) yy[n] = __bfloat162float(y[row * ldy + c]);
             }
     };
     fetch(t0);
     for (int t = t0; t < t1; t += AHEAD) {
         float ca[AHEAD], cs[AHEAD], cy[AHEAD];
 #pragma unroll
-        for (int n = 0; n < AHEAD; ++n) { ca[n] = a[n]; cs[n] = sh[n]; cy[n] = yy[n]; }
+        for (int n = 0; n < AHEAD; ++n) { ca[n] = a[n]; cs[n] = sh[n]; cy[n] = PHASE == 2 ? yy[n] : 0.f; }
         if (t + AHEAD < t1) fetch(t + AHEAD);
 #pragma unroll
         for (int n = 0; n < AHEAD; ++n)
             if (t + n < t1) {
                 S = fmaf(ca[n], S, cs[n]);
-                out[(size_t)(t + n) * ldo + c] = __float2bfloat16_rn(S * gelu_tanh_f(cy[n] + yb));
+                if (PHASE == 0) A *= ca[n];
+                else out[(size_t)(t + n) * ldo + c] = __float2bfloat16_rn(S * cy[n]);
             }
     }
-    state[(size_t)slot * channels + c] = S;
+    if (PHASE == 0) mine[(size_t)ck * channels] = make_float2(A, S);
+}
+
+constexpr int GU_CHUNK = 128;
+SSB_API long long ssb_gated_unit_scan_scratch(int n_seqs, int max_new, int channels) {
+    return 2ll * n_seqs * ((max_new + GU_CHUNK - 1) / GU_CHUNK) * channels;          // floats
 }
 
 SSB_API int ssb_gated_unit_scan_split(float* gates, int ldg, const float* bias_r, const float* bias_i, const float* rate,
-                                      const void* u, int ldu, const void* y, int ldy, const float* y_bias, float* state,
+                                      const void* u, int ldu, void* y, int ldy, const float* y_bias, float* state,
                                       const int* cu_new, const int* seq_slot, void* out, int ldo, int n_seqs, int n_tokens,
-                                      int channels, int block, int pdl, cudaStream_t stream) {
+                                      int max_new, int channels, int block, float* scratch, int pdl, cudaStream_t stream) {
     if (n_seqs <= 0 || n_tokens <= 0) return 0;
-    if (channels <= 0 || block <= 0 || channels % block) return SSB_ERR_BAD_SIZE;
+    if (channels <= 0 || block <= 0 || channels % block || max_new <= 0 || !scratch || ((uintptr_t)scratch & 7)) return SSB_ERR_BAD_SIZE;
     const size_t total = (size_t)n_tokens * channels;
     int rc = ssb_launch(gated_unit_prepare_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, pdl != 0, gates,
-                        ldg, bias_r, bias_i, rate, (const bf16*)u, ldu, channels, block, total);
+                        ldg, bias_r, bias_i, rate, (const bf16*)u, ldu, (bf16*)y, ldy, y_bias, channels, block, total);
     if (!rc) rc = ssb_launch_status();
     if (rc) return rc;
-    const dim3 grid(n_seqs, (channels + 63) / 64);
-    if (grid.y > 65535) return SSB_ERR_BAD_SIZE;
-    rc = ssb_launch(gated_unit_walk_kernel, grid, dim3(64), 0, stream, pdl != 0, (const float*)gates, ldg, (const bf16*)y, ldy,
-                    y_bias, state, cu_new, seq_slot, (bf16*)out, ldo, channels, block);
-    return rc ? rc : ssb_launch_status();
+    const int chunks = (max_new + GU_CHUNK - 1) / GU_CHUNK;
+    const dim3 grid(n_seqs, (channels + 63) / 64, chunks);
+    if (grid.y > 65535 || grid.z > 65535) return SSB_ERR_BAD_SIZE;
+#define SSB_GU(PHASE, GRID) \
+    rc = ssb_launch(gated_unit_walk_kernel<PHASE>, GRID, dim3(64), 0, stream, pdl != 0, (const float*)gates, ldg, (const bf16*)y, \
+                    ldy, state, cu_new, seq_slot, (bf16*)out, ldo, channels, block, GU_CHUNK, chunks, (float2*)scratch); \
+    if (!rc) rc = ssb_launch_status(); \
+    if (rc) return rc
+    SSB_GU(0, grid);
+    SSB_GU(1, dim3(n_seqs, (channels + 63) / 64));
+    SSB_GU(2, grid);
+#undef SSB_GU
+    return 0;
 }
 
 SSB_API int ssb_gated_unit_scan(const float* gates, int ldg, const float* bias_r, const float* bias_i, const float* rate,
