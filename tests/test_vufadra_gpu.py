@@ -213,6 +213,61 @@ def test_sigmoid_attention_kernels_agree(dim, vdim, heads, kv_heads, chunk):
                 assert err < 0.02 * max(1.0, float(want.float().abs().max())), (counts, window, split, err)
 
 
+@pytest.mark.parametrize("kind", ["delta", "bonus"])
+@pytest.mark.parametrize("heads,dim", [(3, 16), (2, 32), (4, 64), (2, 128), (1, 24)])
+def test_matrix_state_walk_forms_agree(kind, heads, dim):
+    """The cp.async form for bfloat16 rows (every register tiling it has) against the float32 form that carries
+    its state in double: three sequences of unequal lengths (one of a single token, none a multiple of four) that
+    continue a state, twice in a row."""
+    from supersonic_b200.csrc import ops
+    g = torch.Generator(device=DEV).manual_seed(dim + heads)
+    HD, counts = heads * dim, [37, 1, 130]
+    T, B = sum(counts), len(counts)
+    cu = torch.tensor([0] + list(np.cumsum(counts)), dtype=torch.int32, device=DEV)
+    slots = torch.tensor([2, 0, 1], dtype=torch.int32, device=DEV)
+    bonus = torch.randn(HD, device=DEV, generator=g) * 0.3
+    state16, state32 = (torch.zeros(3, HD * dim, device=DEV) for _ in range(2))
+    for _ in range(2):
+        proj = (torch.randn(T, 3 * HD + 8, device=DEV, generator=g) * 0.5).bfloat16()
+        log_w = -torch.rand(T, HD, device=DEV, generator=g) * 0.2
+        u = torch.randn(T, heads, dim, device=DEV, generator=g)
+        u = (u / u.norm(dim=-1, keepdim=True)).reshape(T, HD)
+        unit = torch.cat([u, u * torch.rand(T, HD, device=DEV, generator=g)], dim=1).contiguous()
+        out16, out32 = (torch.zeros(T, HD, device=DEV) for _ in range(2))
+        args = dict(unit=unit if kind == "delta" else None, bonus=bonus if kind == "bonus" else None)
+        ops.matrix_state_scan(proj, 0, HD, 2 * HD, log_w.exp(), kind, state16, cu, slots, out16, heads, dim, dim, **args)
+        ops.matrix_state_scan(proj.float(), 0, HD, 2 * HD, log_w, kind, state32, cu, slots, out32, heads, dim, dim, **args)
+        scale = max(1.0, float(out32.abs().max()))
+        assert float((out16 - out32).abs().max()) < 2e-4 * scale, (kind, heads, dim)
+        assert float((state16 - state32).abs().max()) < 2e-4 * max(1.0, float(state32.abs().max()))
+
+
+@pytest.mark.parametrize("channels,block", [(96, 32), (2048, 128), (50, 10)])
+def test_vector_state_walk_forms_agree(channels, block):
+    """The walk over chunks in parallel (bfloat16, long runs) against the single launch in float32: sequences of 1,
+    127, 128 and 300 tokens in one step, continuing a state, twice in a row."""
+    from supersonic_b200.csrc import ops
+    g = torch.Generator(device=DEV).manual_seed(channels)
+    counts = [127, 1, 300, 128]
+    T, B, C = sum(counts), 4, channels
+    cu = torch.tensor([0] + list(np.cumsum(counts)), dtype=torch.int32, device=DEV)
+    slots = torch.tensor([3, 1, 0, 2], dtype=torch.int32, device=DEV)
+    br, bi, yb = (torch.randn(C, device=DEV, generator=g) for _ in range(3))
+    rate = -8.0 * torch.rand(C, device=DEV, generator=g) * 0.2
+    state16, state32 = (torch.zeros(4, C, device=DEV) for _ in range(2))
+    for _ in range(2):
+        gates = torch.randn(T, 2 * C, device=DEV, generator=g)
+        u, y = (torch.randn(T, C, device=DEV, generator=g).bfloat16() for _ in range(2))
+        out16 = torch.empty(T, C, device=DEV, dtype=torch.bfloat16)
+        out32 = torch.empty(T, C, device=DEV)
+        ops.gated_unit_scan(gates.clone(), br, bi, rate, u.float(), y.float(), yb, state32, cu, slots, out32, block)
+        scratch = torch.empty(ops.gated_unit_scan_scratch(B, max(counts), C), device=DEV)
+        ops.gated_unit_scan(gates.clone(), br, bi, rate, u, y.clone(), yb, state16, cu, slots, out16, block,
+                            max_new=max(counts), scratch=scratch)
+        assert float((out16.float() - out32).abs().max()) < 0.02 * max(1.0, float(out32.abs().max()))
+        assert float((state16 - state32).abs().max()) < 1e-4 * max(1.0, float(state32.abs().max()))
+
+
 def test_pair_embedding_and_token_shift_in_a_batch_of_portions():
     """Three sequences whose tokens arrive in unequal portions, several sequences a step: the row picked by the
     token before (the table's last row for a sequence's first token) and the mix with the row before, across
