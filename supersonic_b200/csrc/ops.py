@@ -514,7 +514,7 @@ def matrix_state_scan(proj: torch.Tensor, r_off: int, k_off: int, v_off: int, de
                       n_heads: int, dim: int, vdim: int, unit: Optional[torch.Tensor] = None,
                       bonus: Optional[torch.Tensor] = None, pdl: bool = False) -> None:
     """Per sequence and head over the sequence's new tokens in order, S [dim, vdim] float32 read from and left in
-    ``state[slot]``.  ``"delta"``: S = diag(w) S - (a u)(u^T S) + k v^T, out = S^T r, with ``unit`` = [u | a u] as
+    ``state[slot]`` (kept there as [heads, vdim, dim]: a value column's rows together).  ``"delta"``: S = diag(w) S - (a u)(u^T S) + k v^T, out = S^T r, with ``unit`` = [u | a u] as
     ``state_scan_prepare`` leaves it; ``"bonus"``: out = (S + diag(bonus) k v^T)^T r, then S = diag(w) S + k v^T.
     ``decay`` [T, heads x dim] float32 holds w, or log w if ``proj`` is float32 (that path takes the exponential in
     double and carries the state of a step's tokens in double); r, k (heads x dim) and v (heads x vdim) are columns of ``proj``."""
@@ -654,7 +654,7 @@ def causal_conv(x: torch.Tensor, x_bias: Optional[torch.Tensor], weight: torch.T
     _need(out, "out", x.dtype, 2)
     C, taps = weight.shape
     if taps > CONV_MAX_TAPS or x.shape[1] < C or out.shape[1] < C or out.shape[0] != x.shape[0] \
-            or tail.shape[1] != max(taps - 1, 1) * C and tail.shape[1] != (taps - 1) * C or not weight.is_contiguous() \
+            or tail.shape[1] != (taps - 1) * C or not weight.is_contiguous() \
             or not tail.is_contiguous() or cu_new.shape[0] != seq_slot.shape[0] + 1:
         raise KernelError(f"causal_conv: shapes (up to {CONV_MAX_TAPS} taps)")
     for v in (x_bias, bias):

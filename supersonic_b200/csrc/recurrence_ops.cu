@@ -424,7 +424,7 @@ matrix_state_scan_kernel(const T* __restrict__ proj, int ld, int r_off, int k_of
 #pragma unroll
     for (int r = 0; r < RPL; ++r) {
         const int i = sub * RPL + r;
-        s_reg[r] = (col && i < dim) ? S[(size_t)i * vdim + j0 + cj] : 0.f;
+        s_reg[r] = (col && i < dim) ? S[(size_t)(j0 + cj) * dim + i] : 0.f;
         b_reg[r] = (!DELTA && bonus != nullptr && i < dim) ? bonus[h * dim + i] : 0.f;
     }
     for (int e = tid; e < NV * MS_TOKENS * DIMP; e += MS_THREADS) (&vec[0][0][0])[e] = 0.f;   // the padding stays zero
@@ -528,7 +528,7 @@ matrix_state_scan_kernel(const T* __restrict__ proj, int ld, int r_off, int k_of
 #pragma unroll
     for (int r = 0; r < RPL; ++r) {
         const int i = sub * RPL + r;
-        if (col && i < dim) S[(size_t)i * vdim + j0 + cj] = (float)s_reg[r];
+        if (col && i < dim) S[(size_t)(j0 + cj) * dim + i] = (float)s_reg[r];
     }
 }
 
@@ -563,11 +563,13 @@ matrix_state_scan_async_kernel(const bf16* __restrict__ proj, int ld, int r_off,
 #pragma unroll
     for (int r = 0; r < RPL; ++r) {
         const int i = sub * RPL + r;
-        s_reg[r] = (col && i < dim) ? S[(size_t)i * vdim + j0 + cj] : 0.f;
+        s_reg[r] = (col && i < dim) ? S[(size_t)(j0 + cj) * dim + i] : 0.f;
         b_reg[r] = (!DELTA && bonus != nullptr && i < dim) ? bonus[h * dim + i] : 0.f;
     }
-    for (int e = tid; e < STAGES * STAGE_BYTES / 4; e += MS_THREADS) reinterpret_cast<uint32_t*>(ms_smem)[e] = 0u;
-    __syncthreads();                                     // rows past dim and columns past vdim stay zero
+    if (dim < DIMP || j0 + MS_COLS > vdim) {             // rows past dim and columns past vdim are never copied: they stay zero
+        for (int e = tid; e < STAGES * STAGE_BYTES / 4; e += MS_THREADS) reinterpret_cast<uint32_t*>(ms_smem)[e] = 0u;
+        __syncthreads();
+    }
     // the 16-byte pieces of a stage are the same in every stage but for the token they start from: each thread
     // works out its pieces once (where in a row, which array, where in the stage) and only adds the row offset
     constexpr int NCH = (TOK * (NF * (DIMP / 4) + 2 * (DIMP / 8) + 2) + MS_THREADS - 1) / MS_THREADS;
@@ -697,13 +699,14 @@ matrix_state_scan_async_kernel(const bf16* __restrict__ proj, int ld, int r_off,
 #pragma unroll
     for (int r = 0; r < RPL; ++r) {
         const int i = sub * RPL + r;
-        if (col && i < dim) S[(size_t)i * vdim + j0 + cj] = s_reg[r];
+        if (col && i < dim) S[(size_t)(j0 + cj) * dim + i] = s_reg[r];
     }
 }
 
 // proj [T, ld]: r, k (n_heads x dim) and v (n_heads x vdim) from the given columns; decay [T, ldd] float32
 // (n_heads x dim), for float32 rows their logarithms (what the prepare kernel leaves in either case); kind 0 (delta rule): unit [T, ldu] float32 = [u | a * u]; kind 1: bonus [n_heads x dim]
-// float32 or null; state [slots, n_heads, dim, vdim] float32; out [T, ldo] float32 (n_heads x vdim).
+// float32 or null; state [slots, n_heads, vdim, dim] float32 (a value column's key rows lie together, so that the eight
+// lanes of a column read and write it in one piece); out [T, ldo] float32 (n_heads x vdim).
 SSB_API int ssb_matrix_state_scan(const void* proj, int ld, int dtype, int r_off, int k_off, int v_off,
                                   const float* decay, int ldd, int kind, const float* unit, int ldu, const float* bonus,
                                   float* state, const int* cu_new, const int* seq_slot, float* out, int ldo, int n_seqs,
