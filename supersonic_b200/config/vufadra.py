@@ -339,6 +339,10 @@ class VufadraConfig:
                 shapes[f"{p}.mlp.down"] = [W, mlp["ff"]]
         return shapes
 
+    def ignorable_tensor(self, name: str) -> bool:
+        """Stored tensors that this configuration never reads: the loop's, where no layer is walked more than zero times."""
+        return name in ("loop.in", "loop.step") and not (self.loop is not None and self.loop["times"] > 0)
+
     def is_norm_tensor(self, name: str) -> bool:
         last = name.rsplit(".", 1)[-1]
         return last in ("norm", "norm1", "norm2", "out") or name.endswith((".q.norm", ".k.norm"))

@@ -358,6 +358,16 @@ class FastKernels(PlainKernels):
     def _scan_scratch(self, n, device):
         return self._buffer("unit_scan_chunks", n, torch.float32, device)
 
+    def matrix_state_step(self, proj, r_off, k_off, v_off, g_off, a_off, z, z_bias, decay_kind, decay_scale, a_bias,
+                          unit_eps, kind, bonus, state, batch, norm_w, eps, gate_kind, y, n_heads, dim, vdim) -> bool:
+        if not (batch.is_decode and proj.dtype == torch.bfloat16 and norm_w.dtype == torch.bfloat16
+                and y.dtype == torch.bfloat16 and dim <= ops.SCAN_MAX_DIM):
+            return False
+        ops.matrix_state_step(proj, r_off, k_off, v_off, g_off, a_off, z, z_bias, decay_kind, decay_scale, a_bias, unit_eps,
+                              kind, bonus, state, batch.cu_new, batch.seq_slot, norm_w, eps, gate_kind, y, n_heads, dim, vdim,
+                              pdl=self._chain(batch.n_tokens))
+        return True
+
     def sigmoid_attention(self, q, k_cache, v_cache, batch, page_table, bias, out, n_q, n_kv, dim, vdim, page_shift,
                           chunk, window, scale):
         if ops.sigmoid_attention_mma_ok(q, k_cache, v_cache, out, dim, vdim, page_shift):

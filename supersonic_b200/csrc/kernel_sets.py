@@ -161,6 +161,12 @@ class PlainKernels:
     def _scan_scratch(self, n, device):
         return torch.empty(n, dtype=torch.float32, device=device)
 
+    def matrix_state_step(self, proj, r_off, k_off, v_off, g_off, a_off, z, z_bias, decay_kind, decay_scale, a_bias,
+                          unit_eps, kind, bonus, state, batch, norm_w, eps, gate_kind, y, n_heads, dim, vdim) -> bool:
+        """Decays, the walk and the head norm with its gate of a decode step in one launch, if this set can do it for
+        this case; False means the caller runs the three operations."""
+        return False
+
     def gated_unit_scan(self, gates, bias_r, bias_i, rate, u, y, y_bias, state, batch, out, block):
         scratch = None
         if u.dtype == torch.bfloat16 and batch.max_new >= ops.GATED_UNIT_SPLIT_MIN_NEW:       # a long run: chunks in parallel
@@ -179,6 +185,11 @@ class PlainKernels:
     def shift_mix(self, h, mu, last, batch, out):
         """out[s] = h + (h shifted by one token - h) * mu[s]; ``last`` carries a sequence's last row across steps."""
         ops.shift_mix(h, mu, last, batch.cu_new, batch.seq_slot, out, batch.max_new, pdl=self._chain(batch.n_tokens))
+
+    def tanh_norm_shift(self, x, norm1, norm2, mu, last, batch, mixed, second):
+        """A layer's entry in one pass: the first tanh norm with the token shift behind it, and the second tanh norm."""
+        ops.tanh_norm_shift(x, norm1, norm2, mu, last, batch.cu_new, batch.seq_slot, mixed, second, batch.max_new,
+                            pdl=self._chain(batch.n_tokens))
 
     def causal_conv(self, x, x_bias, weight, bias, tail, batch, out):
         ops.causal_conv(x, x_bias, weight, bias, tail, batch.cu_new, batch.seq_slot, out, batch.max_new,

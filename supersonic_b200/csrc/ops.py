@@ -546,6 +546,41 @@ GATED_UNIT_SPLIT_MIN_NEW = 64    # runs of new tokens from which the vector-stat
 GATED_UNIT_CHUNK = 128
 
 
+def matrix_state_step(proj: torch.Tensor, r_off: int, k_off: int, v_off: int, g_off: int, a_off: int, z: torch.Tensor,
+                      z_bias: torch.Tensor, decay_kind: str, decay_scale: float, a_bias: Optional[torch.Tensor],
+                      unit_eps: float, kind: str, bonus: Optional[torch.Tensor], state: torch.Tensor, cu_new: torch.Tensor,
+                      seq_slot: torch.Tensor, norm_w: torch.Tensor, eps: float, gate_kind: str, y: torch.Tensor,
+                      n_heads: int, dim: int, vdim: int, pdl: bool = False) -> None:
+    """A decode step of a matrix-state recurrence in one launch, for bfloat16 projections and one new token a sequence:
+    ``state_scan_prepare`` (``z`` is read, not overwritten), ``matrix_state_scan`` and ``head_norm_gate`` of every
+    sequence's token; ``y`` gets the normed and gated head outputs."""
+    _need(proj, "proj", torch.bfloat16, 2); _need(z, "z", torch.float32, 2); _need(z_bias, "z_bias", torch.float32, 1)
+    _need(state, "state", torch.float32, 2); _need(y, "y", torch.bfloat16, 2); _need(norm_w, "norm_w", torch.bfloat16, 1)
+    _need(cu_new, "cu_new", torch.int32, 1); _need(seq_slot, "seq_slot", torch.int32, 1)
+    T, B, HD = proj.shape[0], seq_slot.shape[0], n_heads * dim
+    if z.shape[0] != T or y.shape[0] != T or z.shape[1] < HD or y.shape[1] < n_heads * vdim or z_bias.shape[0] != HD \
+            or cu_new.shape[0] != B + 1 or max(r_off, k_off) + HD > proj.shape[1] \
+            or max(v_off, g_off) + n_heads * vdim > proj.shape[1] or norm_w.shape[0] not in (vdim, n_heads * vdim):
+        raise KernelError("matrix_state_step: sizes")
+    if state.shape[1] != HD * vdim or not state.is_contiguous() or dim > SCAN_MAX_DIM:
+        raise KernelError(f"matrix_state_step: state rows of heads x dim x vdim, dim up to {SCAN_MAX_DIM}")
+    if kind == "delta":
+        _need(a_bias, "a_bias", torch.float32, 1)
+        if a_bias.shape[0] != HD or a_off + HD > proj.shape[1]:
+            raise KernelError("matrix_state_step: the removal's pre-activation and bias")
+    if bonus is not None:
+        _need(bonus, "bonus", torch.float32)
+        if bonus.numel() != HD or not bonus.is_contiguous():
+            raise KernelError("matrix_state_step: one bonus per head and key channel")
+    w_stride = vdim if norm_w.shape[0] == n_heads * vdim and n_heads > 1 else 0
+    _check(_fn("recurrence_ops", "ssb_matrix_state_step")(
+        _ptr(proj), c_int(proj.stride(0)), c_int(r_off), c_int(k_off), c_int(v_off), c_int(g_off), c_int(a_off), _ptr(z),
+        c_int(z.stride(0)), _ptr(z_bias), c_int(DECAY_KINDS[decay_kind]), c_float(decay_scale), _ptr(a_bias),
+        c_float(unit_eps), c_int(STATE_SCAN_KINDS[kind]), _ptr(bonus), _ptr(state), _ptr(cu_new), _ptr(seq_slot),
+        _ptr(norm_w), c_int(w_stride), c_float(eps), c_int(GATE_KINDS[gate_kind]), _ptr(y), c_int(y.stride(0)), c_int(B),
+        c_int(n_heads), c_int(dim), c_int(vdim), c_int(1 if pdl else 0), _stream()), "matrix_state_step")
+
+
 def gated_unit_scan_scratch(n_seqs: int, max_new: int, channels: int) -> int:
     """float32 elements of scratch the chunked walk needs: (A, B) per sequence, chunk and channel."""
     return 2 * n_seqs * (-(-max_new // GATED_UNIT_CHUNK)) * channels
@@ -640,6 +675,33 @@ def shift_mix(h: torch.Tensor, mu: torch.Tensor, last: torch.Tensor, cu_new: tor
         _ptr(h), c_int(h.stride(0)), c_int(dtype_code(h.dtype)), _ptr(mu), c_int(mu.shape[0]), _ptr(last), _ptr(cu_new),
         _ptr(seq_slot), _ptr(out), c_longlong(T * W), c_int(W), c_int(seq_slot.shape[0]), c_int(max_new), c_int(W),
         c_int(1 if pdl else 0), _stream()), "shift_mix")
+
+
+def tanh_norm_shift(x: torch.Tensor, norm1, norm2, mu: torch.Tensor, last: torch.Tensor, cu_new: torch.Tensor,
+                    seq_slot: torch.Tensor, mixed: torch.Tensor, second: Optional[torch.Tensor], max_new: int,
+                    pdl: bool = False) -> None:
+    """``dynamic_tanh`` with ``norm1 = (alpha, weight, bias)`` followed by ``shift_mix`` with the one mix ``mu`` into
+    ``mixed``, and ``dynamic_tanh`` with ``norm2`` of the same rows into ``second`` (None: no second norm), in one
+    pass over ``x``."""
+    _need(x, "x", torch.float32, 2); _need(mu, "mu", torch.float32); _need(last, "last", torch.float32, 2)
+    _need(mixed, "mixed", None, 2)
+    T, W = x.shape
+    vecs = list(norm1) + (list(norm2) if second is not None else [])
+    for v in vecs:
+        _need(v, "norm tensor", torch.float32, 1)
+    if not x.is_contiguous() or tuple(mixed.shape) != (T, W) or not mixed.is_contiguous() or mu.numel() != W \
+            or last.shape[1] != W or not last.is_contiguous() or cu_new.shape[0] != seq_slot.shape[0] + 1 \
+            or any(v.numel() != (1 if i % 3 == 0 else W) for i, v in enumerate(vecs)):
+        raise KernelError("tanh_norm_shift: shapes")
+    if second is not None:
+        _need(second, "second", mixed.dtype, 2)
+        if tuple(second.shape) != (T, W) or not second.is_contiguous():
+            raise KernelError("tanh_norm_shift: shapes of the second norm's output")
+    a2, w2, b2 = norm2 if second is not None else (None, None, None)
+    _check(_fn("sequence_ops", "ssb_tanh_norm_shift")(
+        _ptr(x), _ptr(norm1[0]), _ptr(norm1[1]), _ptr(norm1[2]), _ptr(a2), _ptr(w2), _ptr(b2), _ptr(mu), _ptr(last),
+        _ptr(cu_new), _ptr(seq_slot), _ptr(mixed), _ptr(second), c_int(dtype_code(mixed.dtype)), c_int(seq_slot.shape[0]),
+        c_int(max_new), c_int(W), c_int(1 if pdl else 0), _stream()), "tanh_norm_shift")
 
 
 CONV_MAX_TAPS = 16

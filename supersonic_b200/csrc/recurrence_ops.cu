@@ -760,6 +760,185 @@ SSB_API int ssb_matrix_state_scan(const void* proj, int ld, int dtype, int r_off
 }
 
 // ---------------------------------------------------------------------------------------
+// One token a sequence (a decode step), bfloat16 projections: what `state_scan_prepare`, the walk and
+// `head_norm_gate` do in three launches, in one.  A block takes a sequence and a head: it makes the head's decays
+// (and unit key and removal vector) in shared memory, walks the state's value columns 16 at a time (eight lanes a
+// column as in the walk above, the state read and written once), and norms and gates the head's output.
+// ---------------------------------------------------------------------------------------
+template <int RPL, bool DELTA>
+__global__ void __launch_bounds__(MS_THREADS)
+matrix_state_step_kernel(const bf16* __restrict__ proj, int ld, int r_off, int k_off, int v_off, int g_off, int a_off,
+                         const float* __restrict__ z, int ldz, const float* __restrict__ z_bias, int decay_kind,
+                         float decay_scale, const float* __restrict__ a_bias, float unit_eps,
+                         const float* __restrict__ bonus, float* __restrict__ state, const int* __restrict__ cu_new,
+                         const int* __restrict__ seq_slot, const bf16* __restrict__ norm_w, int w_stride, float eps,
+                         int gate_kind, bf16* __restrict__ y, int ldy, int n_heads, int dim, int vdim) {
+    constexpr int DIMP = MS_LANES * RPL;
+    extern __shared__ __align__(16) float st_smem[];
+    float* w_s = st_smem;                                // [DIMP] each: decay, key, receptance, unit key, removal
+    float* k_s = w_s + DIMP;
+    float* r_s = k_s + DIMP;
+    float* u_s = r_s + DIMP;
+    float* au_s = u_s + DIMP;
+    float* o_s = au_s + DIMP;                            // [vdim] the head's output
+    __shared__ float red[MS_THREADS / 32];
+    const int b = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, sub = tid % MS_LANES, cj = tid / MS_LANES;
+    ssb_pdl_launch_dependents();
+    ssb_pdl_wait();
+    const int slot = seq_slot[b];
+    if (slot < 0) return;
+    const size_t t = (size_t)cu_new[b];
+    const bf16* row = proj + t * ld;
+    float ksq = 0.f;
+    for (int i = tid; i < DIMP; i += MS_THREADS) {
+        float w = 0.f, k = 0.f, r = 0.f;
+        if (i < dim) {
+            const float zv = z[t * ldz + h * dim + i] + z_bias[h * dim + i];
+            w = expf(decay_kind == 0 ? -expf(zv) : -decay_scale / (1.0f + expf(-zv)));
+            k = __bfloat162float(row[k_off + h * dim + i]);
+            r = __bfloat162float(row[r_off + h * dim + i]);
+        }
+        w_s[i] = w;
+        k_s[i] = k;
+        r_s[i] = r;
+        ksq = fmaf(k, k, ksq);
+    }
+    if (DELTA) {
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) ksq += __shfl_xor_sync(0xffffffffu, ksq, m);
+        if ((tid & 31) == 0) red[tid >> 5] = ksq;
+        __syncthreads();
+        float tot = 0.f;
+#pragma unroll
+        for (int wv = 0; wv < MS_THREADS / 32; ++wv) tot += red[wv];
+        const float inv = 1.0f / sqrtf(tot + unit_eps);
+        for (int i = tid; i < DIMP; i += MS_THREADS) {
+            float u = 0.f, au = 0.f;
+            if (i < dim) {
+                u = k_s[i] * inv;
+                au = u / (1.0f + expf(-(__bfloat162float(row[a_off + h * dim + i]) + a_bias[h * dim + i])));
+            }
+            u_s[i] = u;
+            au_s[i] = au;
+        }
+    }
+    __syncthreads();
+    float* S = state + ((size_t)slot * n_heads + h) * dim * vdim;
+    float b_reg[RPL];
+#pragma unroll
+    for (int r = 0; r < RPL; ++r) {
+        const int i = sub * RPL + r;
+        b_reg[r] = (!DELTA && bonus != nullptr && i < dim) ? bonus[h * dim + i] : 0.f;
+    }
+    // several tiles of 16 columns at a time, all their state on its way before the first is worked on
+    constexpr int GROUP = RPL <= 8 ? 4 : RPL == 16 ? 2 : 1;
+    for (int j0 = 0; j0 < vdim; j0 += GROUP * MS_COLS) {
+        float s_all[GROUP][RPL], v_all[GROUP];
+#pragma unroll
+        for (int gi = 0; gi < GROUP; ++gi) {
+            const int c = j0 + gi * MS_COLS + cj;
+            const bool col = c < vdim;
+#pragma unroll
+            for (int r = 0; r < RPL; ++r) {
+                const int i = sub * RPL + r;
+                s_all[gi][r] = (col && i < dim) ? S[(size_t)c * dim + i] : 0.f;
+            }
+            v_all[gi] = col ? __bfloat162float(row[v_off + h * vdim + c]) : 0.f;
+        }
+#pragma unroll
+        for (int gi = 0; gi < GROUP; ++gi) {
+            const int c = j0 + gi * MS_COLS + cj;
+            const bool col = c < vdim;
+            float* s_reg = s_all[gi];
+            const float v = v_all[gi];
+            float o = 0.f;
+            if (DELTA) {
+                float seen = 0.f;
+#pragma unroll
+                for (int r = 0; r < RPL; ++r) seen = fmaf(u_s[sub * RPL + r], s_reg[r], seen);
+                seen += __shfl_xor_sync(0xffffffffu, seen, 1);
+                seen += __shfl_xor_sync(0xffffffffu, seen, 2);
+                seen += __shfl_xor_sync(0xffffffffu, seen, 4);
+#pragma unroll
+                for (int r = 0; r < RPL; ++r) {
+                    const int i = sub * RPL + r;
+                    s_reg[r] = fmaf(w_s[i], s_reg[r], fmaf(k_s[i], v, -au_s[i] * seen));
+                    o = fmaf(s_reg[r], r_s[i], o);
+                }
+            } else {
+#pragma unroll
+                for (int r = 0; r < RPL; ++r) {
+                    const int i = sub * RPL + r;
+                    const float kv = k_s[i] * v;
+                    o = fmaf(fmaf(b_reg[r], kv, s_reg[r]), r_s[i], o);
+                    s_reg[r] = fmaf(w_s[i], s_reg[r], kv);
+                }
+            }
+            o += __shfl_xor_sync(0xffffffffu, o, 1);
+            o += __shfl_xor_sync(0xffffffffu, o, 2);
+            o += __shfl_xor_sync(0xffffffffu, o, 4);
+            if (col) {
+                if (sub == 0) o_s[c] = o;
+#pragma unroll
+                for (int r = 0; r < RPL; ++r) {
+                    const int i = sub * RPL + r;
+                    if (i < dim) S[(size_t)c * dim + i] = s_reg[r];
+                }
+            }
+        }
+    }
+    __syncthreads();
+    // the head's output over its root mean square, weighted and gated
+    float part = 0.f;
+    for (int c = tid; c < vdim; c += MS_THREADS) part = fmaf(o_s[c], o_s[c], part);
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) part += __shfl_xor_sync(0xffffffffu, part, m);
+    __syncthreads();                                     // red is read above by everyone before it is written again
+    if ((tid & 31) == 0) red[tid >> 5] = part;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int wv = 0; wv < MS_THREADS / 32; ++wv) tot += red[wv];
+    const float inv = 1.0f / sqrtf(tot / (float)vdim + eps);
+    for (int c = tid; c < vdim; c += MS_THREADS) {
+        const float gv = __bfloat162float(row[g_off + h * vdim + c]);
+        const float sg = 1.0f / (1.0f + expf(-gv));
+        const float ga = gate_kind == 0 ? gv * sg : gate_kind == 1 ? sg : gv;
+        y[t * ldy + h * vdim + c] = __float2bfloat16_rn(o_s[c] * inv * __bfloat162float(norm_w[(size_t)h * w_stride + c]) * ga);
+    }
+}
+
+SSB_API int ssb_matrix_state_step(const void* proj, int ld, int r_off, int k_off, int v_off, int g_off, int a_off,
+                                  const float* z, int ldz, const float* z_bias, int decay_kind, float decay_scale,
+                                  const float* a_bias, float unit_eps, int kind, const float* bonus, float* state,
+                                  const int* cu_new, const int* seq_slot, const void* norm_w, int w_stride, float eps,
+                                  int gate_kind, void* y, int ldy, int n_seqs, int n_heads, int dim, int vdim, int pdl,
+                                  cudaStream_t stream) {
+    if (n_seqs <= 0) return 0;
+    if (dim <= 0 || dim > 256 || vdim <= 0 || n_heads <= 0 || n_heads > 65535 || (kind != 0 && kind != 1) ||
+        decay_kind < 0 || decay_kind > 1 || gate_kind < 0 || gate_kind > 2 || (kind == 0 && a_bias == nullptr))
+        return SSB_ERR_BAD_SIZE;
+    const dim3 grid(n_seqs, n_heads);
+    int rc = 0;
+#define SSB_ST(RPL, DELTA) \
+    rc = ssb_launch(matrix_state_step_kernel<RPL, DELTA>, grid, dim3(MS_THREADS), (size_t)(5 * MS_LANES * RPL + vdim) * sizeof(float), \
+                    stream, pdl != 0, (const bf16*)proj, ld, r_off, k_off, v_off, g_off, a_off, z, ldz, z_bias, decay_kind, \
+                    decay_scale, a_bias, unit_eps, bonus, state, cu_new, seq_slot, (const bf16*)norm_w, w_stride, eps, gate_kind, \
+                    (bf16*)y, ldy, n_heads, dim, vdim)
+#define SSB_ST_DIM(DELTA) do { \
+        if (dim <= 32) SSB_ST(4, DELTA); \
+        else if (dim <= 64) SSB_ST(8, DELTA); \
+        else if (dim <= 128) SSB_ST(16, DELTA); \
+        else SSB_ST(32, DELTA); \
+    } while (0)
+    if (vdim > 8192) return SSB_ERR_BAD_SIZE;
+    if (kind == 0) SSB_ST_DIM(true); else SSB_ST_DIM(false);
+#undef SSB_ST_DIM
+#undef SSB_ST
+    return rc ? rc : ssb_launch_status();
+}
+
+// ---------------------------------------------------------------------------------------
 // The real-gated linear recurrent unit: a state value per channel,
 //     r = sigmoid(g_r + b_r), i = sigmoid(g_i + b_i), log a = rate * r (rate = -8 softplus(lambda) < 0),
 //     S_t = a S_(t-1) + sqrt(1 - a^2) * i * u_t,        out_t = S_t * gelu_tanh(y_t + y_bias)

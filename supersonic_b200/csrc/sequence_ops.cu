@@ -163,6 +163,70 @@ SSB_API int ssb_shift_mix(const void* h, int ldh, int dtype, const float* mu, in
 }
 
 // ---------------------------------------------------------------------------------------
+// The entry of a layer with two tanh norms and a token shift in one pass over the stream: with
+// n1 = tanh(a1 x) w1 + b1 (rounded to the activation type, as the norm alone leaves it),
+//     mixed[t] = n1[t] + (n1[t-1] - n1[t]) * mu        (n1[-1] from `last[slot]`, which then keeps the step's last n1)
+//     second[t] = tanh(a2 x[t]) w2 + b2                 (if a second norm is given)
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(SEQ_THREADS)
+tanh_norm_shift_kernel(const float* __restrict__ x, const float* __restrict__ alpha1, const float* __restrict__ w1,
+                       const float* __restrict__ b1, const float* __restrict__ alpha2, const float* __restrict__ w2,
+                       const float* __restrict__ b2, const float* __restrict__ mu, float* __restrict__ last,
+                       const int* __restrict__ cu_new, const int* __restrict__ seq_slot, T* __restrict__ mixed,
+                       T* __restrict__ second, int width, int tile) {
+    const int b = blockIdx.x, tid = threadIdx.x;
+    ssb_pdl_launch_dependents();
+    ssb_pdl_wait();
+    const int slot = seq_slot[b];
+    if (slot < 0) return;
+    const int t0 = cu_new[b], t1 = cu_new[b + 1];
+    const int lo = t0 + blockIdx.y * tile, hi = min(t1, lo + tile);
+    if (lo >= hi) return;
+    const float a1 = alpha1[0], a2 = second ? alpha2[0] : 0.f;
+    for (int c = blockIdx.z * SEQ_THREADS + tid; c < width; c += gridDim.z * SEQ_THREADS) {
+        const float w1c = w1[c], b1c = b1[c], muc = mu[c];
+        auto first = [&](size_t t) { return ssb_to_float(ssb_from_float<T>(fmaf(tanhf(a1 * x[t * width + c]), w1c, b1c))); };
+        float before;
+        if (lo == t0) {
+            float* keep = last + (size_t)slot * width + c;
+            before = *keep;
+            *keep = first((size_t)(t1 - 1));
+        } else {
+            before = first((size_t)(lo - 1));
+        }
+        for (int t = lo; t < hi; ++t) {
+            const float xv = x[(size_t)t * width + c];
+            const float cur = ssb_to_float(ssb_from_float<T>(fmaf(tanhf(a1 * xv), w1c, b1c)));
+            mixed[(size_t)t * width + c] = ssb_from_float<T>(fmaf(before - cur, muc, cur));
+            if (second) second[(size_t)t * width + c] = ssb_from_float<T>(fmaf(tanhf(a2 * xv), w2[c], b2[c]));
+            before = cur;
+        }
+    }
+}
+
+SSB_API int ssb_tanh_norm_shift(const float* x, const float* alpha1, const float* w1, const float* b1, const float* alpha2,
+                                const float* w2, const float* b2, const float* mu, float* last, const int* cu_new,
+                                const int* seq_slot, void* mixed, void* second, int dtype, int n_seqs, int max_new, int width,
+                                int pdl, cudaStream_t stream) {
+    if (n_seqs <= 0 || max_new <= 0) return 0;
+    if (width <= 0 || (second && !(alpha2 && w2 && b2))) return SSB_ERR_BAD_SIZE;
+    const int tile = 8;
+    const dim3 grid(n_seqs, (max_new + tile - 1) / tile, min((width + SEQ_THREADS - 1) / SEQ_THREADS, 64));
+    if (grid.y > 65535) return SSB_ERR_BAD_SIZE;
+    int rc;
+    if (dtype == SSB_F32)
+        rc = ssb_launch(tanh_norm_shift_kernel<float>, grid, dim3(SEQ_THREADS), 0, stream, pdl != 0, x, alpha1, w1, b1, alpha2, w2,
+                        b2, mu, last, cu_new, seq_slot, (float*)mixed, (float*)second, width, tile);
+    else if (dtype == SSB_BF16)
+        rc = ssb_launch(tanh_norm_shift_kernel<bf16>, grid, dim3(SEQ_THREADS), 0, stream, pdl != 0, x, alpha1, w1, b1, alpha2, w2,
+                        b2, mu, last, cu_new, seq_slot, (bf16*)mixed, (bf16*)second, width, tile);
+    else
+        return SSB_ERR_BAD_DTYPE;
+    return rc ? rc : ssb_launch_status();
+}
+
+// ---------------------------------------------------------------------------------------
 // A causal convolution per channel over a few taps: with in[t] = x[t] + x_bias,
 //     u[t][c] = bias[c] + sum_j w[c][j] * in[t - (taps - 1 - j)][c]
 // (the last column multiplies the current token).  Inputs from before the step come from

@@ -104,6 +104,20 @@ class ParallelBlock:
             elif ctx.streams is None:
                 raise RuntimeError("a depth-averaging layer ran before the first one of its step")
             residual = ctx.streams[self.index + 1]
+        fused = self.shift is not None and hasattr(self.mixer_norm, "with_shift") and \
+            (self.feed_forward is None or type(self.feed_forward_norm) is type(self.mixer_norm))
+        if fused:
+            # both norms and the shift read the entering stream once (a norm kind that offers this form)
+            if not writes_cache:
+                raise ValueError("a block with token shift keeps state: its stop must write its cache entry")
+            mixed, n2 = self.mixer_norm.with_shift(ctx, residual, self.shift_mu, ctx.cache.state((cache_id, "shift")),
+                                                   self.feed_forward_norm if self.feed_forward is not None else None)
+            ctx.stage = "mixer"
+            self.mixer.forward(ctx, mixed, residual, (cache_id, "mixer"), writes_cache, self.position)
+            if self.feed_forward is not None:
+                ctx.stage = "feed_forward"
+                self.feed_forward.forward(ctx, n2, residual)
+            return self._after(ctx)
         x = NormedInput(ctx, residual, self.mixer_norm)
         x2 = x
         if self.feed_forward is not None and self.feed_forward_norm is not None:
@@ -123,6 +137,9 @@ class ParallelBlock:
         if self.feed_forward is not None:
             ctx.stage = "feed_forward"
             self.feed_forward.forward(ctx, self._give(x2, self.feed_forward), residual)
+        return self._after(ctx)
+
+    def _after(self, ctx):
         if self.depth is None:
             return None
         out = ctx.streams[self.index + 2]

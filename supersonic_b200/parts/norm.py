@@ -81,3 +81,14 @@ class DynamicTanh:
         out = torch.empty((n, self.size), dtype=self.dtype, device=x.device)
         ctx.kernels.dynamic_tanh(x, self.alpha, self.weight, self.bias, out, rows)
         return out
+
+    def with_shift(self, ctx, x, mu, last, second=None):
+        """This norm of ``x`` with a token shift behind it (``mu`` [1, size], ``last``: the per-slot row that carries a
+        sequence's last normed row), and the norm ``second`` (another of this kind, or None) of the same ``x``, in
+        one pass: returns (shifted, second's output or None)."""
+        mixed = torch.empty((x.shape[0], self.size), dtype=self.dtype, device=x.device)
+        other = torch.empty_like(mixed) if second is not None else None
+        ctx.kernels.tanh_norm_shift(x, (self.alpha, self.weight, self.bias),
+                                    None if second is None else (second.alpha, second.weight, second.bias), mu, last,
+                                    ctx.batch, mixed, other)
+        return mixed, other

@@ -151,13 +151,18 @@ class DeltaRule:
         k.tanh_(proj[:, self.z_off:])
         z = torch.empty((T, HD), dtype=torch.float32, device=dev)
         k.linear(proj[:, self.z_off:], self.w2, z)
+        y = torch.empty((T, HD), dtype=self.dtype, device=dev)
+        if k.matrix_state_step(proj, self.r_off, self.k_off, self.v_off, self.g_off, self.a_off, z, self.w0, "exp_sigmoid",
+                               self.decay_scale, self.a_bias, self.unit_eps, "delta", None, ctx.cache.state(cache_id),
+                               ctx.batch, self.norm_w, self.eps, "sigmoid", y, H, d, d):
+            k.linear(y, self.w_o, residual, accumulate=True)       # a decode step: decays, walk, norm and gate in one launch
+            return
         unit = torch.empty((T, 2 * HD), dtype=torch.float32, device=dev)
         k.state_scan_prepare(z, self.w0, "exp_sigmoid", self.decay_scale, H, d, proj, self.k_off, self.a_off,
                              self.a_bias, self.unit_eps, unit, log_decay=self.dtype == torch.float32)
         o = torch.empty((T, HD), dtype=torch.float32, device=dev)
         k.matrix_state_scan(proj, self.r_off, self.k_off, self.v_off, z, "delta", ctx.cache.state(cache_id), ctx.batch,
                             o, H, d, d, unit=unit)
-        y = torch.empty((T, HD), dtype=self.dtype, device=dev)
         k.head_norm_gate(o, self.norm_w, self.eps, proj[:, self.g_off:], y, H, d, gate_kind="sigmoid")
         k.linear(y, self.w_o, residual, accumulate=True)
 
@@ -218,10 +223,15 @@ class TimeMixing:
         k.tanh_(proj[:, self.z_off:])
         z = torch.empty((T, HD), dtype=torch.float32, device=dev)
         k.linear(proj[:, self.z_off:], self.w2, z)
+        y = torch.empty((T, HD), dtype=self.dtype, device=dev)
+        if k.matrix_state_step(proj, self.r_off, self.k_off, self.v_off, self.g_off, 0, z, self.w0, "double_exp", 1.0, None,
+                               0.0, "bonus", self.bonus, ctx.cache.state((cache_id, "state")), ctx.batch, self.norm_w,
+                               self.eps, "silu", y, H, d, d):
+            k.linear(y, self.w_o, residual, accumulate=True)
+            return
         k.state_scan_prepare(z, self.w0, "double_exp", 1.0, H, d, log_decay=self.dtype == torch.float32)
         o = torch.empty((T, HD), dtype=torch.float32, device=dev)
         k.matrix_state_scan(proj, self.r_off, self.k_off, self.v_off, z, "bonus", ctx.cache.state((cache_id, "state")),
                             ctx.batch, o, H, d, d, bonus=self.bonus)
-        y = torch.empty((T, HD), dtype=self.dtype, device=dev)
         k.head_norm_gate(o, self.norm_w, self.eps, proj[:, self.g_off:], y, H, d, gate_kind="silu")
         k.linear(y, self.w_o, residual, accumulate=True)

@@ -35,7 +35,9 @@ def test_schedule_walks_the_loop_with_a_cache_entry_per_run():
     assert [(s.layer, s.before) for s in plain.schedule] == [(0, None), (1, None), (2, None)] and not plain.adapters
     zero = copy.deepcopy(tv.A)
     zero["loop"]["times"] = 0
-    assert not config_from_dict(zero).build_spec().adapters
+    unlooped = config_from_dict(zero)
+    assert not unlooped.build_spec().adapters and unlooped.ignorable_tensor("loop.in")
+    assert not config_from_dict(tv.A).ignorable_tensor("loop.in")
 
 
 def test_parts_and_their_parameters():

@@ -242,6 +242,43 @@ def test_matrix_state_walk_forms_agree(kind, heads, dim):
         assert float((state16 - state32).abs().max()) < 2e-4 * max(1.0, float(state32.abs().max()))
 
 
+@pytest.mark.parametrize("kind", ["delta", "bonus"])
+@pytest.mark.parametrize("heads,dim", [(3, 20), (2, 32), (4, 64), (2, 128), (1, 200)])
+def test_decode_step_in_one_launch_agrees_with_the_three_operations(kind, heads, dim):
+    """Decays, walk, head norm and gate of one token a sequence in one launch against the three launches, over
+    three steps that continue a state (one row is padding)."""
+    from supersonic_b200.csrc import ops
+    g = torch.Generator(device=DEV).manual_seed(dim * 3 + heads)
+    HD, B = heads * dim, 4
+    cu = torch.arange(B + 1, dtype=torch.int32, device=DEV)
+    slots = torch.tensor([2, -1, 0, 1], dtype=torch.int32, device=DEV)
+    z_bias = torch.randn(HD, device=DEV, generator=g) - (3.0 if kind == "delta" else 0.0)
+    a_bias, bonus = torch.randn(HD, device=DEV, generator=g), torch.randn(HD, device=DEV, generator=g) * 0.3
+    norm_w = (1 + 0.1 * torch.randn(HD, device=DEV, generator=g)).bfloat16()
+    one, three = (torch.zeros(3, HD * dim, device=DEV) for _ in range(2))
+    decay_kind, scale, gate = ("exp_sigmoid", 0.6, "sigmoid") if kind == "delta" else ("double_exp", 1.0, "silu")
+    offs = [i * HD for i in range(5)]                      # r, k, v, g, a
+    for _ in range(3):
+        proj = (torch.randn(B, 5 * HD, device=DEV, generator=g) * 0.5).bfloat16()
+        z = torch.randn(B, HD, device=DEV, generator=g)
+        y1, y3 = (torch.zeros(B, HD, device=DEV, dtype=torch.bfloat16) for _ in range(2))
+        ops.matrix_state_step(proj, offs[0], offs[1], offs[2], offs[3], offs[4], z.clone(), z_bias, decay_kind, scale,
+                              a_bias if kind == "delta" else None, 1e-6, kind, bonus if kind == "bonus" else None, one, cu,
+                              slots, norm_w, 1e-5, gate, y1, heads, dim, dim)
+        zz, unit, o = z.clone(), torch.zeros(B, 2 * HD, device=DEV), torch.zeros(B, HD, device=DEV)
+        if kind == "delta":
+            ops.state_scan_prepare(zz, z_bias, decay_kind, scale, heads, dim, proj, offs[1], offs[4], a_bias, 1e-6, unit)
+        else:
+            ops.state_scan_prepare(zz, z_bias, decay_kind, scale, heads, dim)
+        ops.matrix_state_scan(proj, offs[0], offs[1], offs[2], zz, kind, three, cu, slots, o, heads, dim, dim,
+                              unit=unit if kind == "delta" else None, bonus=bonus if kind == "bonus" else None)
+        ops.head_norm_gate(o, norm_w, 1e-5, proj[:, offs[3]:], y3, heads, dim, gate_kind=gate)
+        live = slots >= 0
+        assert float((y1[live].float() - y3[live].float()).abs().max()) < 0.02 * max(1.0, float(y3[live].float().abs().max()))
+        assert float((one - three).abs().max()) < 1e-5 * max(1.0, float(three.abs().max()))
+    assert float(one.abs().max()) > 0
+
+
 @pytest.mark.parametrize("channels,block", [(96, 32), (2048, 128), (50, 10)])
 def test_vector_state_walk_forms_agree(channels, block):
     """The walk over chunks in parallel (bfloat16, long runs) against the single launch in float32: sequences of 1,
@@ -311,6 +348,35 @@ def test_pair_embedding_and_token_shift_in_a_batch_of_portions():
             assert float((torch.cat([m[s] for m in got_m[i]]).double() - want).abs().max()) < 1e-5
     # a sequence's first token takes the last row of the pair table
     assert torch.equal(torch.cat(got_e[0])[0], (plain["embed"][seqs[0][0]].float() + plain["bigram"][-1].float()))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_norms_and_shift_in_one_pass_equal_the_three_operations(dtype):
+    """Both tanh norms and the token shift in one launch give the bits of norm, shift and norm one after the other,
+    over two steps of unequal portions that carry the last row (one sequence of a single token)."""
+    from supersonic_b200.csrc import ops
+    g = torch.Generator(device=DEV).manual_seed(5)
+    W, counts = 200, [19, 1, 40]
+    T = sum(counts)
+    cu = torch.tensor([0] + list(np.cumsum(counts)), dtype=torch.int32, device=DEV)
+    slots = torch.tensor([1, 2, 0], dtype=torch.int32, device=DEV)
+    n1, n2 = ([torch.rand(1, device=DEV, generator=g) + 0.3, torch.randn(W, device=DEV, generator=g),
+               torch.randn(W, device=DEV, generator=g)] for _ in range(2))
+    mu = torch.rand(1, W, device=DEV, generator=g)
+    last_a, last_b = (torch.zeros(3, W, device=DEV) for _ in range(2))
+    for _ in range(2):
+        x = torch.randn(T, W, device=DEV, generator=g) * 2
+        mixed, second = (torch.empty(T, W, device=DEV, dtype=dtype) for _ in range(2))
+        ops.tanh_norm_shift(x, n1, n2, mu, last_a, cu, slots, mixed, second, max(counts))
+        a, b, m = torch.empty(T, W, device=DEV, dtype=dtype), torch.empty(T, W, device=DEV, dtype=dtype), torch.empty(1, T, W, device=DEV, dtype=dtype)
+        ops.dynamic_tanh(x, n1[0], n1[1], n1[2], a)
+        ops.dynamic_tanh(x, n2[0], n2[1], n2[2], b)
+        ops.shift_mix(a, mu, last_b, cu, slots, m, max(counts))
+        assert torch.equal(mixed, m[0]) and torch.equal(second, b) and torch.equal(last_a, last_b)
+        only = torch.empty(T, W, device=DEV, dtype=dtype)
+        keep = last_a.clone()
+        ops.tanh_norm_shift(x, n1, None, mu, keep, cu, slots, only, None, max(counts))
+        assert float(only.float().abs().max()) > 0
 
 
 def test_stream_after_every_layer_run():
