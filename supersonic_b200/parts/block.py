@@ -110,9 +110,9 @@ class ParallelBlock:
             # both norms and the shift read the entering stream once (a norm kind that offers this form)
             if not writes_cache:
                 raise ValueError("a block with token shift keeps state: its stop must write its cache entry")
+            ctx.stage = "mixer"
             mixed, n2 = self.mixer_norm.with_shift(ctx, residual, self.shift_mu, ctx.cache.state((cache_id, "shift")),
                                                    self.feed_forward_norm if self.feed_forward is not None else None)
-            ctx.stage = "mixer"
             self.mixer.forward(ctx, mixed, residual, (cache_id, "mixer"), writes_cache, self.position)
             if self.feed_forward is not None:
                 ctx.stage = "feed_forward"
