@@ -536,21 +536,24 @@ matrix_state_scan_kernel(const T* __restrict__ proj, int ld, int r_off, int k_of
 // a stage go from global to shared memory by cp.async in the types they are stored in (decays and unit keys
 // float32, r, k and v bfloat16), four stages deep, so that the loads of the next twelve tokens are in flight
 // while four are worked on, with one barrier per four tokens.  (With the vectors staged through registers the
-// walk waited on global memory at every turn: four warps an SM hide nothing.)
-template <int RPL, bool DELTA>
+// walk waited on global memory at every turn: four warps an SM hide nothing.)  LANES lanes share a column: sixteen
+// where a head has 64 key channels or more (a lane's share of a token is then half as many instructions, and the
+// walk is bound by the instructions one warp issues a token), eight otherwise.
+template <int LANES, int RPL, bool DELTA>
 __global__ void __launch_bounds__(MS_THREADS)
 matrix_state_scan_async_kernel(const bf16* __restrict__ proj, int ld, int r_off, int k_off, int v_off,
                                const float* __restrict__ decay, int ldd, const float* __restrict__ unit, int ldu,
                                const float* __restrict__ bonus, float* __restrict__ state,
                                const int* __restrict__ cu_new, const int* __restrict__ seq_slot,
                                float* __restrict__ out, int ldo, int n_heads, int dim, int vdim) {
-    constexpr int DIMP = MS_LANES * RPL, STAGES = 4, TOK = MS_TOKENS;
+    constexpr int COLS = MS_THREADS / LANES;              // value columns a block owns: 16 with eight lanes a column, 8 with sixteen
+    constexpr int DIMP = LANES * RPL, STAGES = 4, TOK = MS_TOKENS;
     constexpr int NF = DELTA ? 3 : 1;                    // float32 vectors a token: w (, u, a * u)
-    constexpr int F_BYTES = NF * TOK * DIMP * 4, KR_BYTES = 2 * TOK * DIMP * 2, V_BYTES = TOK * MS_COLS * 2;
+    constexpr int F_BYTES = NF * TOK * DIMP * 4, KR_BYTES = 2 * TOK * DIMP * 2, V_BYTES = TOK * COLS * 2;
     constexpr int STAGE_BYTES = F_BYTES + KR_BYTES + V_BYTES;
     extern __shared__ __align__(16) unsigned char ms_smem[];
-    const int b = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * MS_COLS;
-    const int tid = threadIdx.x, sub = tid % MS_LANES, cj = tid / MS_LANES;
+    const int b = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * COLS;
+    const int tid = threadIdx.x, sub = tid % LANES, cj = tid / LANES;
     ssb_pdl_launch_dependents();
     ssb_pdl_wait();
     const int slot = seq_slot[b];
@@ -566,14 +569,15 @@ matrix_state_scan_async_kernel(const bf16* __restrict__ proj, int ld, int r_off,
         s_reg[r] = (col && i < dim) ? S[(size_t)(j0 + cj) * dim + i] : 0.f;
         b_reg[r] = (!DELTA && bonus != nullptr && i < dim) ? bonus[h * dim + i] : 0.f;
     }
-    if (dim < DIMP || j0 + MS_COLS > vdim) {             // rows past dim and columns past vdim are never copied: they stay zero
+    if (dim < DIMP || j0 + COLS > vdim) {             // rows past dim and columns past vdim are never copied: they stay zero
         for (int e = tid; e < STAGES * STAGE_BYTES / 4; e += MS_THREADS) reinterpret_cast<uint32_t*>(ms_smem)[e] = 0u;
         __syncthreads();
     }
     // the 16-byte pieces of a stage are the same in every stage but for the token they start from: each thread
     // works out its pieces once (where in a row, which array, where in the stage) and only adds the row offset
-    constexpr int NCH = (TOK * (NF * (DIMP / 4) + 2 * (DIMP / 8) + 2) + MS_THREADS - 1) / MS_THREADS;
-    const int cf = dim / 4, cb = dim / 8, per_tok = NF * cf + 2 * cb + 2;
+    constexpr int VP = COLS / 8;                           // 16-byte pieces of a token's value columns
+    constexpr int NCH = (TOK * (NF * (DIMP / 4) + 2 * (DIMP / 8) + VP) + MS_THREADS - 1) / MS_THREADS;
+    const int cf = dim / 4, cb = dim / 8, per_tok = NF * cf + 2 * cb + VP;
     const unsigned char* c_src[NCH];
     long long c_step[NCH];                               // bytes from a row to the next in the piece's array
     int c_dst[NCH], c_tt[NCH];                           // c_tt = TOK: no piece
@@ -604,7 +608,7 @@ matrix_state_scan_async_kernel(const bf16* __restrict__ proj, int ld, int r_off,
             if (j0 + e * 8 >= vdim) continue;
             c_step[n] = (long long)ld * 2;
             c_src[n] = reinterpret_cast<const unsigned char*>(proj + v_off + h * vdim + j0 + e * 8) + (size_t)(t0 + tt) * c_step[n];
-            c_dst[n] = F_BYTES + KR_BYTES + (tt * MS_COLS + e * 8) * 2;
+            c_dst[n] = F_BYTES + KR_BYTES + (tt * COLS + e * 8) * 2;
         }
         c_tt[n] = tt;
     }
@@ -638,7 +642,7 @@ matrix_state_scan_async_kernel(const bf16* __restrict__ proj, int ld, int r_off,
         for (int tt = 0; tt < TOK; ++tt) {
             o_part[tt] = 0.f;
             if (tt >= n_tok) continue;                   // only a sequence's last stage is short
-            const float v = __bfloat162float(vs[tt * MS_COLS + cj]);
+            const float v = __bfloat162float(vs[tt * COLS + cj]);
             const float* wv = fv + tt * DIMP + sub * RPL;
             const __nv_bfloat162* k2 = reinterpret_cast<const __nv_bfloat162*>(kr + tt * DIMP + sub * RPL);
             const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(kr + (TOK + tt) * DIMP + sub * RPL);
@@ -656,9 +660,8 @@ matrix_state_scan_async_kernel(const bf16* __restrict__ proj, int ld, int r_off,
                     seen1 = fmaf(u.w, s_reg[r + 3], seen1);
                 }
                 float seen = seen0 + seen1;
-                seen += __shfl_xor_sync(0xffffffffu, seen, 1);
-                seen += __shfl_xor_sync(0xffffffffu, seen, 2);
-                seen += __shfl_xor_sync(0xffffffffu, seen, 4);
+#pragma unroll
+                for (int m = 1; m < LANES; m <<= 1) seen += __shfl_xor_sync(0xffffffffu, seen, m);
 #pragma unroll
                 for (int r = 0; r < RPL; r += 4) {
                     const float4 w = *reinterpret_cast<const float4*>(wv + r), au = *reinterpret_cast<const float4*>(auv + r);
@@ -685,11 +688,9 @@ matrix_state_scan_async_kernel(const bf16* __restrict__ proj, int ld, int r_off,
             o_part[tt] = o0 + o1;
         }
 #pragma unroll
-        for (int tt = 0; tt < TOK; ++tt) o_part[tt] += __shfl_xor_sync(0xffffffffu, o_part[tt], 1);
+        for (int m = 1; m < LANES; m <<= 1)
 #pragma unroll
-        for (int tt = 0; tt < TOK; ++tt) o_part[tt] += __shfl_xor_sync(0xffffffffu, o_part[tt], 2);
-#pragma unroll
-        for (int tt = 0; tt < TOK; ++tt) o_part[tt] += __shfl_xor_sync(0xffffffffu, o_part[tt], 4);
+            for (int tt = 0; tt < TOK; ++tt) o_part[tt] += __shfl_xor_sync(0xffffffffu, o_part[tt], m);
         if (sub == 0 && col)
 #pragma unroll
             for (int tt = 0; tt < TOK; ++tt)
@@ -722,20 +723,22 @@ SSB_API int ssb_matrix_state_scan(const void* proj, int ld, int dtype, int r_off
                         k_off % 8 == 0 && v_off % 8 == 0 && ldd % 4 == 0 && (kind != 0 || ldu % 4 == 0) &&
                         !(((uintptr_t)proj | (uintptr_t)decay | (uintptr_t)unit) & 15);
     if (pieces) {
-#define SSB_MSA(RPL, DELTA) do { \
-        constexpr int stage = ((DELTA ? 3 : 1) * MS_TOKENS * MS_LANES * RPL * 4) + 2 * MS_TOKENS * MS_LANES * RPL * 2 + MS_TOKENS * MS_COLS * 2; \
-        auto kern = matrix_state_scan_async_kernel<RPL, DELTA>; \
+#define SSB_MSA(LANES, RPL, DELTA) do { \
+        constexpr int cols = MS_THREADS / LANES; \
+        constexpr int stage = ((DELTA ? 3 : 1) * MS_TOKENS * LANES * RPL * 4) + 2 * MS_TOKENS * LANES * RPL * 2 + MS_TOKENS * cols * 2; \
+        auto kern = matrix_state_scan_async_kernel<LANES, RPL, DELTA>; \
         if (4 * stage > 48 * 1024) { \
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * stage); \
             if (e != cudaSuccess) return (int)e; \
         } \
-        rc = ssb_launch(kern, grid, dim3(MS_THREADS), (size_t)4 * stage, stream, pdl != 0, (const bf16*)proj, ld, r_off, k_off, v_off, \
+        const dim3 g2(n_seqs, n_heads, (vdim + cols - 1) / cols); \
+        rc = ssb_launch(kern, g2, dim3(MS_THREADS), (size_t)4 * stage, stream, pdl != 0, (const bf16*)proj, ld, r_off, k_off, v_off, \
                         decay, ldd, unit, ldu, bonus, state, cu_new, seq_slot, out, ldo, n_heads, dim, vdim); \
     } while (0)
 #define SSB_MSA_DIM(DELTA) do { \
-        if (dim <= 32) SSB_MSA(4, DELTA); \
-        else if (dim <= 64) SSB_MSA(8, DELTA); \
-        else SSB_MSA(16, DELTA); \
+        if (dim <= 32) SSB_MSA(8, 4, DELTA); \
+        else if (dim <= 64) SSB_MSA(16, 4, DELTA); \
+        else SSB_MSA(16, 8, DELTA); \
     } while (0)
         if (kind == 0) SSB_MSA_DIM(true); else SSB_MSA_DIM(false);
 #undef SSB_MSA_DIM
